@@ -2,7 +2,7 @@
 
 The reference allocates one (K, V) pair of tensors per layer (core/src/worker/cache_engine.rs:107-160)
 with a layout made for its decode kernel.  Here every group of layers has ONE tensor
-[call, page, 2 (k, v), kv_head, slot, head_dim]: a page number addresses the same page in every
+[call, page, planes (k and v, or one vector that is both), kv_head, slot, head_dim]: a page number addresses the same page in every
 layer of its group, and one (page, kv_head) holds block_size * head_dim contiguous values.
 """
 from __future__ import annotations
@@ -23,7 +23,7 @@ class GroupLayout:
 
     def page_bytes(self, block_size: int, dtype: torch.dtype) -> int:
         """Bytes of one page over all layers of the group (cf. core/src/worker/cache_engine.rs:88-105)."""
-        return len(self.calls) * 2 * self.spec.num_kv_heads * self.spec.head_dim * block_size * \
+        return len(self.calls) * self.spec.planes * self.spec.num_kv_heads * self.spec.head_dim * block_size * \
             torch.empty(0, dtype=dtype).element_size()
 
 
@@ -74,7 +74,7 @@ class CacheStorage:
         self.num_blocks = list(num_blocks)
         self.num_state_slots = num_state_slots
         # one page more than the pool knows: the "null page" that stand-in requests of a padded batch write to
-        self.tensors = [torch.zeros((len(gl.calls), n + 1, 2, gl.spec.num_kv_heads, block_size, gl.spec.head_dim),
+        self.tensors = [torch.zeros((len(gl.calls), n + 1, gl.spec.planes, gl.spec.num_kv_heads, block_size, gl.spec.head_dim),
                                     dtype=dtype, device=device) for gl, n in zip(self.groups, num_blocks)]
         self.null_pages = list(num_blocks)
         self.layer_caches: List[LayerCache] = []

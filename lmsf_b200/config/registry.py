@@ -45,10 +45,12 @@ def registered_architectures() -> List[str]:
 def resolve_architecture(config_dict: Dict[str, Any]) -> Architecture:
     _load_builtin()
     names = list(config_dict.get("architectures") or [])
+    if isinstance(config_dict.get("architecture"), str):      # some designs name themselves in the singular
+        names.append(config_dict["architecture"])
     if config_dict.get("model_type"):
         names.append(config_dict["model_type"])
     if not names:
-        raise ConfigError("config.json names neither 'architectures' nor 'model_type'")
+        raise ConfigError("config.json names neither 'architectures', 'architecture' nor 'model_type'")
     for n in names:
         arch = _ARCHITECTURES.get(str(n).lower())
         if arch is not None:

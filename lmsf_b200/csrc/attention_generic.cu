@@ -32,6 +32,8 @@ struct GenericAttnArgs {
   int n_q_heads, n_kv_heads, head_dim;
   float softcap;                               // > 0: scores become softcap * tanh(score / softcap) before the softmax
   const float* slopes;                         // [n_q_heads] or null: slope * (key position - query position) is added to the scores
+  int shared_kv;                               // 1: a page holds one vector per token that is key and value at once ([page][1][kv_head][slot][hd])
+  const void* gate; long long gate_stride;     // [n_tokens, n_q_heads] or null: head h's output is multiplied by sigmoid(gate[t, h])
 };
 
 template <typename T>
@@ -53,7 +55,7 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
   __syncthreads();
 
   const size_t head_off = (size_t)kvh * a.block_size * hd;
-  const size_t v_off = (size_t)a.n_kv_heads * a.block_size * hd;
+  const size_t v_off = a.shared_kv ? 0 : (size_t)a.n_kv_heads * a.block_size * hd;
   const int nd = (hd + 31) / 32;
 
   float m = -INFINITY, l = 0.f;
@@ -116,10 +118,11 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
     L = fmaf(part_l[w], f[w], L);
   }
   T* o = (T*)a.out + (size_t)t * a.out_stride + (size_t)head * hd;
+  const float g = a.gate ? 1.0f / (1.0f + expf(-to_f32(((const T*)a.gate)[(size_t)t * a.gate_stride + head]))) : 1.0f;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float v = 0.f;
     for (int w = 0; w < kWarps; ++w) v = fmaf(part_acc[w][d], f[w], v);
-    o[d] = from_f32<T>(v / L);
+    o[d] = from_f32<T>(a.gate ? (v / L) * g : v / L);
   }
 }
 
@@ -129,11 +132,15 @@ __global__ void __launch_bounds__(kWarps * 32) attention_generic_kernel(GenericA
 // are capped smoothly, softcap * tanh(score / softcap).  slopes ([n_q_heads] float32, may be null): a position encoding
 // by a bias that grows with distance, slope[head] * (key position - query position), added to the scaled score as the
 // reference's decode kernel adds it (vllm/kernels/attention/attention_kernels.cu:144-145, :232-234).
-LMSF_API int lmsf_attention_generic_scores(const void* q, long long q_stride, void* out, long long out_stride,
-                                           const void* cache, long long page_stride, const int* block_table, int max_blocks,
-                                           int block_size, const int* token_seq, const int* positions, float scale,
-                                           float softcap, const float* slopes, int window, int n_tokens, int n_q_heads,
-                                           int n_kv_heads, int head_dim, int dtype, void* stream) {
+// shared_kv = 1: the cache holds one vector per token and kv head, [page][1][kv_head][slot][head_dim], which is read as
+// the key and as the value (attention over a cached low-rank vector).  gate ([n_tokens, n_q_heads] of `dtype`, row stride
+// gate_stride, may be null): head h's output of token t is multiplied by sigmoid(gate[t, h]).
+LMSF_API int lmsf_attention_generic_ext(const void* q, long long q_stride, void* out, long long out_stride,
+                                        const void* cache, long long page_stride, const int* block_table, int max_blocks,
+                                        int block_size, const int* token_seq, const int* positions, float scale,
+                                        float softcap, const float* slopes, int window, int n_tokens, int n_q_heads,
+                                        int n_kv_heads, int head_dim, int dtype, int shared_kv, const void* gate,
+                                        long long gate_stride, void* stream) {
   using namespace lmsf;
   if (n_tokens <= 0) return 0;
   if (head_dim <= 0 || head_dim > kMaxHeadDim || head_dim % 16)
@@ -144,12 +151,23 @@ LMSF_API int lmsf_attention_generic_scores(const void* q, long long q_stride, vo
   if (block_size <= 0 || max_blocks <= 0) LMSF_REFUSE("attention: bad block table geometry");
   if (dtype != LMSF_F32 && dtype != LMSF_BF16) LMSF_REFUSE("attention: unknown dtype code %d", dtype);
   GenericAttnArgs a{q, q_stride, out, out_stride, cache, page_stride, block_table, max_blocks, block_size,
-                    token_seq, positions, scale, window, n_q_heads, n_kv_heads, head_dim, softcap > 0.f ? softcap : 0.f, slopes};
+                    token_seq, positions, scale, window, n_q_heads, n_kv_heads, head_dim, softcap > 0.f ? softcap : 0.f, slopes,
+                    shared_kv ? 1 : 0, gate, gate_stride};
   dim3 grid(n_tokens, n_q_heads);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == LMSF_F32) attention_generic_kernel<float><<<grid, kWarps * 32, 0, s>>>(a);
   else attention_generic_kernel<bf16><<<grid, kWarps * 32, 0, s>>>(a);
   return LMSF_LAUNCH_STATUS();
+}
+
+LMSF_API int lmsf_attention_generic_scores(const void* q, long long q_stride, void* out, long long out_stride,
+                                           const void* cache, long long page_stride, const int* block_table, int max_blocks,
+                                           int block_size, const int* token_seq, const int* positions, float scale,
+                                           float softcap, const float* slopes, int window, int n_tokens, int n_q_heads,
+                                           int n_kv_heads, int head_dim, int dtype, void* stream) {
+  return lmsf_attention_generic_ext(q, q_stride, out, out_stride, cache, page_stride, block_table, max_blocks, block_size,
+                                    token_seq, positions, scale, softcap, slopes, window, n_tokens, n_q_heads, n_kv_heads,
+                                    head_dim, dtype, 0, nullptr, 0, stream);
 }
 
 LMSF_API int lmsf_attention_generic(const void* q, long long q_stride, void* out, long long out_stride,

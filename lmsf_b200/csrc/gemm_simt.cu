@@ -16,11 +16,15 @@ constexpr int BM = 64, BN = 64, BK = 16;
 template <typename TA, typename TC>
 __global__ void __launch_bounds__(256) gemm_tn_kernel(TC* __restrict__ C, const TA* __restrict__ A,
                                                       const TA* __restrict__ W, int M, int N, int K, long long lda,
-                                                      long long ldw, long long ldc) {
+                                                      long long ldw, long long ldc, long long batch_a,
+                                                      long long batch_w, long long batch_c) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  A += (size_t)blockIdx.z * batch_a;   // one product per blockIdx.z (a head, for instance); all strides 0 for one product
+  W += (size_t)blockIdx.z * batch_w;
+  C += (size_t)blockIdx.z * batch_c;
   const int tx = tid % 16, ty = tid / 16;  // thread's 4x4 patch: rows ty*4.., cols tx*4..
   const int lr = tid / 4, lk = (tid % 4) * 4;  // loader: row lr of the tile, k offsets lk..lk+3
 
@@ -67,23 +71,32 @@ __global__ void __launch_bounds__(256) gemm_tn_kernel(TC* __restrict__ C, const 
 
 }  // namespace lmsf
 
+// `batch` products in one launch: product b reads A + b * batch_a and W + b * batch_w and writes C + b * batch_c
+// (elements).  The heads of one activation matrix are such a batch: batch_a = head size, lda = the row stride.
 // in_dtype: type of A and W; out_dtype: type of C.  Leading dimensions in elements.
-LMSF_API int lmsf_gemm_tn_simt(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
-                               long long ldw, long long ldc, int in_dtype, int out_dtype, void* stream) {
+LMSF_API int lmsf_gemm_tn_simt_batched(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
+                                       long long ldw, long long ldc, int batch, long long batch_a, long long batch_w,
+                                       long long batch_c, int in_dtype, int out_dtype, void* stream) {
   using namespace lmsf;
-  if (M <= 0 || N <= 0) return 0;
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
   if (K <= 0) LMSF_REFUSE("gemm: K=%d must be positive", K);
   if (lda < K || ldw < K || ldc < N) LMSF_REFUSE("gemm: a leading dimension is smaller than its row");
-  dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
+  if (batch > 65535) LMSF_REFUSE("gemm: more than 65535 products in one launch");
+  dim3 grid(ceil_div(N, BN), ceil_div(M, BM), batch);
   if (grid.y > 65535) LMSF_REFUSE("gemm: M=%d is too large for one launch", M);
   cudaStream_t s = (cudaStream_t)stream;
   if (in_dtype == LMSF_F32 && out_dtype == LMSF_F32)
-    gemm_tn_kernel<float, float><<<grid, 256, 0, s>>>((float*)C, (const float*)A, (const float*)W, M, N, K, lda, ldw, ldc);
+    gemm_tn_kernel<float, float><<<grid, 256, 0, s>>>((float*)C, (const float*)A, (const float*)W, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
   else if (in_dtype == LMSF_BF16 && out_dtype == LMSF_BF16)
-    gemm_tn_kernel<bf16, bf16><<<grid, 256, 0, s>>>((bf16*)C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldw, ldc);
+    gemm_tn_kernel<bf16, bf16><<<grid, 256, 0, s>>>((bf16*)C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
   else if (in_dtype == LMSF_BF16 && out_dtype == LMSF_F32)
-    gemm_tn_kernel<bf16, float><<<grid, 256, 0, s>>>((float*)C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldw, ldc);
+    gemm_tn_kernel<bf16, float><<<grid, 256, 0, s>>>((float*)C, (const bf16*)A, (const bf16*)W, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
   else
     LMSF_REFUSE("gemm: unsupported dtype pair (in %d, out %d)", in_dtype, out_dtype);
   return LMSF_LAUNCH_STATUS();
+}
+
+LMSF_API int lmsf_gemm_tn_simt(void* C, const void* A, const void* W, int M, int N, int K, long long lda,
+                               long long ldw, long long ldc, int in_dtype, int out_dtype, void* stream) {
+  return lmsf_gemm_tn_simt_batched(C, A, W, M, N, K, lda, ldw, ldc, 1, 0, 0, 0, in_dtype, out_dtype, stream);
 }

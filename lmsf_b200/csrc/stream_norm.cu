@@ -1,0 +1,163 @@
+// Norms around a float32 residual stream, for blocks that norm a branch before AND after it
+// (x <- x + scale * norm_post(branch(norm_pre(x)))), and the embedding that is normed before it enters the stream.
+//
+// One kernel does what lies between two branches:
+//   res <- res + norm(y) * w_post * layer_scale      (the branch just computed, if there is one)
+//   res <- res + first + vec                          (what a repeated span of layers adds at its entry, if given)
+//   h    = norm(res) * w_next                         (the input of the next branch, if asked for)
+// Every sum, root and product is float32; y and h have the activation type.  One block per token; the row is held
+// in registers between the passes (up to kMaxPerThread values per thread), so y and res are read once.
+#include "common.cuh"
+
+LMSF_DEFINE_LAST_ERROR(lmsf_stream_norm)
+
+namespace lmsf {
+
+constexpr int kThreads = 256;
+constexpr int kMaxPerThread = 64;   // widths up to 16,384
+
+template <typename T, int PER>
+__global__ void __launch_bounds__(kThreads) stream_norm_kernel(float* __restrict__ res, const T* __restrict__ y,
+                                                               const float* __restrict__ w_post, const float* __restrict__ ls,
+                                                               const float* __restrict__ first, const float* __restrict__ vec,
+                                                               T* __restrict__ h, const float* __restrict__ w_next,
+                                                               int hidden, float eps_post, float eps_next) {
+  __shared__ float scratch[33];
+  const size_t base = (size_t)blockIdx.x * hidden;
+  float v[PER];
+  float r[PER];
+  pdl_launch_dependents();
+  pdl_wait();
+  float ss = 0.f;
+  if (y != nullptr) {
+#pragma unroll
+    for (int it = 0; it < PER; ++it) {
+      const int i = it * kThreads + threadIdx.x;
+      v[it] = i < hidden ? to_f32(y[base + i]) : 0.f;
+      ss = fmaf(v[it], v[it], ss);
+    }
+    ss = block_sum(ss, scratch);
+  }
+  const float inv_post = 1.0f / sqrtf(ss / (float)hidden + eps_post);
+  float s2 = 0.f;
+#pragma unroll
+  for (int it = 0; it < PER; ++it) {
+    const int i = it * kThreads + threadIdx.x;
+    float x = 0.f;
+    if (i < hidden) {
+      x = res[base + i];
+      if (y != nullptr) {
+        float b = (v[it] * inv_post) * w_post[i];
+        if (ls != nullptr) b *= ls[i];
+        x += b;
+      }
+      if (first != nullptr) x += first[base + i];
+      if (vec != nullptr) x += vec[i];
+      if (y != nullptr || first != nullptr || vec != nullptr) res[base + i] = x;
+    }
+    r[it] = x;
+    s2 = fmaf(x, x, s2);
+  }
+  if (h == nullptr) return;
+  s2 = block_sum(s2, scratch);
+  const float inv = 1.0f / sqrtf(s2 / (float)hidden + eps_next);
+#pragma unroll
+  for (int it = 0; it < PER; ++it) {
+    const int i = it * kThreads + threadIdx.x;
+    if (i < hidden) h[base + i] = from_f32<T>((r[it] * inv) * w_next[i]);
+  }
+}
+
+// res[t] = norm(table[ids[t]]) * w (float32), and a second copy in `keep` when it is not null.
+// An id outside the vocabulary writes zeros and raises the error flag.
+template <typename T, int PER>
+__global__ void __launch_bounds__(kThreads) embed_norm_kernel(float* __restrict__ res, float* __restrict__ keep,
+                                                              const T* __restrict__ table, const int* __restrict__ ids,
+                                                              const float* __restrict__ w, int hidden, int vocab, float eps,
+                                                              float scale, int* __restrict__ error_flag) {
+  __shared__ float scratch[33];
+  const int id = ids[blockIdx.x];
+  const bool ok = id >= 0 && id < vocab;
+  if (!ok && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
+  const T* src = table + (size_t)(ok ? id : 0) * hidden;
+  const size_t base = (size_t)blockIdx.x * hidden;
+  float v[PER];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < PER; ++it) {
+    const int i = it * kThreads + threadIdx.x;
+    v[it] = (ok && i < hidden) ? to_f32(src[i]) * scale : 0.f;
+    ss = fmaf(v[it], v[it], ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+  for (int it = 0; it < PER; ++it) {
+    const int i = it * kThreads + threadIdx.x;
+    if (i < hidden) {
+      const float o = ok ? (v[it] * inv) * w[i] : 0.f;
+      res[base + i] = o;
+      if (keep != nullptr) keep[base + i] = o;
+    }
+  }
+}
+
+template <typename T, int PER>
+static int launch_stream(float* res, const void* y, const float* w_post, const float* ls, const float* first,
+                         const float* vec, void* h, const float* w_next, int n, int hidden, float eps_post, float eps_next,
+                         cudaStream_t s) {
+  return launch_pdl(stream_norm_kernel<T, PER>, dim3(n), dim3(kThreads), 0, s, res, (const T*)y, w_post, ls, first, vec,
+                    (T*)h, w_next, hidden, eps_post, eps_next);
+}
+
+template <typename T>
+static int pick_stream(int per, float* res, const void* y, const float* w_post, const float* ls, const float* first,
+                       const float* vec, void* h, const float* w_next, int n, int hidden, float eps_post, float eps_next,
+                       cudaStream_t s) {
+#define LMSF_CASE(P) if (per <= P) return launch_stream<T, P>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s)
+  LMSF_CASE(1); LMSF_CASE(2); LMSF_CASE(4); LMSF_CASE(8); LMSF_CASE(16); LMSF_CASE(32); LMSF_CASE(64);
+#undef LMSF_CASE
+  return LMSF_EBADARG;
+}
+
+}  // namespace lmsf
+
+// res: float32 [n, hidden].  y ([n, hidden] of `dtype`, with float32 w_post [hidden] and optional float32 ls [hidden]),
+// first (float32 [n, hidden]), vec (float32 [hidden]) and h ([n, hidden] of `dtype`, with float32 w_next) may each be null.
+LMSF_API int lmsf_stream_norm(float* res, const void* y, const float* w_post, const float* ls, const float* first,
+                              const float* vec, void* h, const float* w_next, int n, int hidden, float eps_post,
+                              float eps_next, int dtype, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (hidden <= 0 || hidden > kThreads * kMaxPerThread) LMSF_REFUSE("stream_norm: width %d is outside 1..%d", hidden, kThreads * kMaxPerThread);
+  if (y != nullptr && w_post == nullptr) LMSF_REFUSE("stream_norm: a branch needs the weight of its norm");
+  if (h != nullptr && w_next == nullptr) LMSF_REFUSE("stream_norm: an output needs the weight of its norm");
+  if ((y != nullptr && !(eps_post > 0.f)) || (h != nullptr && !(eps_next > 0.f))) LMSF_REFUSE("stream_norm: eps must be positive");
+  const int per = ceil_div(hidden, kThreads);
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc;
+  if (dtype == LMSF_F32) rc = pick_stream<float>(per, res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s);
+  else if (dtype == LMSF_BF16) rc = pick_stream<bf16>(per, res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s);
+  else LMSF_REFUSE("stream_norm: unknown dtype code %d", dtype);
+  return rc;
+}
+
+// res (and keep, if not null): float32 [n, hidden] = norm(table[ids] * scale) * w; table: [vocab, hidden] of `dtype`.
+LMSF_API int lmsf_embed_norm(float* res, float* keep, const void* table, const int* ids, const float* w, int n, int hidden,
+                             int vocab, float eps, float scale, int dtype, int* error_flag, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (hidden <= 0 || hidden > kThreads * kMaxPerThread) LMSF_REFUSE("embed_norm: width %d is outside 1..%d", hidden, kThreads * kMaxPerThread);
+  if (!(eps > 0.f)) LMSF_REFUSE("embed_norm: eps must be positive");
+  const int per = ceil_div(hidden, kThreads);
+  cudaStream_t s = (cudaStream_t)stream;
+#define LMSF_CASE(T, P)                                                                                              \
+  if (per <= P) {                                                                                                    \
+    embed_norm_kernel<T, P><<<n, kThreads, 0, s>>>(res, keep, (const T*)table, ids, w, hidden, vocab, eps, scale, error_flag); \
+    return LMSF_LAUNCH_STATUS();                                                                                     \
+  }
+  if (dtype == LMSF_F32) { LMSF_CASE(float, 1) LMSF_CASE(float, 2) LMSF_CASE(float, 4) LMSF_CASE(float, 8) LMSF_CASE(float, 16) LMSF_CASE(float, 32) LMSF_CASE(float, 64) }
+  else if (dtype == LMSF_BF16) { LMSF_CASE(bf16, 1) LMSF_CASE(bf16, 2) LMSF_CASE(bf16, 4) LMSF_CASE(bf16, 8) LMSF_CASE(bf16, 16) LMSF_CASE(bf16, 32) LMSF_CASE(bf16, 64) }
+#undef LMSF_CASE
+  LMSF_REFUSE("embed_norm: unknown dtype code %d", dtype);
+}

@@ -698,3 +698,248 @@ def attention_prefill_tc(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor
            _i32(tile_q0, "tile_q0"), n_tiles, _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale),
            int(window or 0), n_q_heads, head_dim, _i32(error_flag, "error_flag"), _stream())
     _check(rc, "attention_tc.cu", "lmsf_attention_tc", d)
+
+
+# ----------------------------------------------------------------------------- norms around a float32 residual stream
+
+def _f32vec(t: Optional[torch.Tensor], n: int, name: str) -> Optional[int]:
+    if t is None:
+        return None
+    if t.dtype != torch.float32 or t.shape != (n,) or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous float32 vector of {n} values")
+    return _ptr(t)
+
+
+def stream_norm(res: torch.Tensor, y: Optional[torch.Tensor] = None, w_post: Optional[torch.Tensor] = None,
+                layer_scale: Optional[torch.Tensor] = None, eps_post: float = 0.0, first: Optional[torch.Tensor] = None,
+                vec: Optional[torch.Tensor] = None, h: Optional[torch.Tensor] = None, w_next: Optional[torch.Tensor] = None,
+                eps_next: float = 0.0):
+    """What lies between two branches of a block that norms a branch before and after it, in one kernel, float32 inside:
+    res += norm(y) * w_post * layer_scale (if y); res += first + vec (whichever is given); h = norm(res) * w_next (if h).
+    res, first: float32 [n, hidden]; y, h: [n, hidden] of the activation type; the vectors are float32 [hidden]."""
+    n, hidden = res.shape
+    if res.dtype != torch.float32 or not res.is_contiguous():
+        raise KernelError("stream_norm: the residual stream must be contiguous float32")
+    act = y if y is not None else h
+    for name, t in (("y", y), ("h", h)):
+        if t is not None and (t.shape != res.shape or not t.is_contiguous() or t.dtype != act.dtype):
+            raise KernelError(f"stream_norm: {name} must be contiguous, of the stream's shape and of one activation type")
+    if first is not None and (first.dtype != torch.float32 or first.shape != res.shape or not first.is_contiguous()):
+        raise KernelError("stream_norm: `first` must be contiguous float32 of the stream's shape")
+    if act is None and first is None and vec is None:
+        return
+    f = _func("stream_norm.cu", "lmsf_stream_norm",
+              [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+               c_float, c_int, c_void_p])
+    rc = f(_ptr(res), _ptr(y), _f32vec(w_post, hidden, "w_post"), _f32vec(layer_scale, hidden, "layer_scale"), _ptr(first),
+           _f32vec(vec, hidden, "vec"), _ptr(h), _f32vec(w_next, hidden, "w_next"), n, hidden, float(eps_post),
+           float(eps_next), dtype_code(act.dtype) if act is not None else F32, _stream())
+    _check(rc, "stream_norm.cu", "lmsf_stream_norm")
+
+
+def embed_norm(res: torch.Tensor, keep: Optional[torch.Tensor], table: torch.Tensor, ids: torch.Tensor, w: torch.Tensor,
+               eps: float, scale: float = 1.0, error_flag: Optional[torch.Tensor] = None):
+    """res[t] = norm(table[ids[t]] * scale) * w in float32 (and the same again in `keep`, if given)."""
+    n, hidden = res.shape
+    if res.dtype != torch.float32 or not res.is_contiguous() or table.shape[1] != hidden or not table.is_contiguous():
+        raise KernelError("embed_norm: res must be contiguous float32 [n, hidden] and the table [vocab, hidden]")
+    if keep is not None and (keep.dtype != torch.float32 or keep.shape != res.shape or not keep.is_contiguous()):
+        raise KernelError("embed_norm: `keep` must be like res")
+    f = _func("stream_norm.cu", "lmsf_embed_norm",
+              [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p])
+    rc = f(_ptr(res), _ptr(keep), _ptr(table), _i32(ids, "ids"), _f32vec(w, hidden, "w"), n, hidden, table.shape[0],
+           float(eps), float(scale), dtype_code(table.dtype), _i32(error_flag, "error_flag"), _stream())
+    _check(rc, "stream_norm.cu", "lmsf_stream_norm")
+
+
+# ----------------------------------------------------------------------------- linear attention with a decay per head
+
+LIGHTNING_ACTS = {None: 0, "none": 0, "silu": 1}
+LIGHTNING_MAX_DK = 256
+
+
+def lightning_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor,
+                   decay: torch.Tensor, cu_q: torch.Tensor, state_slot: torch.Tensor, n_seqs: int, heads: int, dk: int,
+                   dv: int, act: Optional[str] = "silu"):
+    """Per request (tokens cu_q[s]..cu_q[s+1]) and head: S = decay S + act(k_t) act(v_t)^T, out_t = S^T act(q_t), with
+    S = state[state_slot[s], head] (float32 [dk, dv]) read before and written after.  q, k: [n, heads * dk] and
+    v: [n, heads * dv] views with a contiguous last dimension; out: float32 [n, heads * dv]."""
+    n = q.shape[0]
+    for name, t, width in (("q", q, heads * dk), ("k", k, heads * dk), ("v", v, heads * dv)):
+        if t.dim() != 2 or t.shape != (n, width) or t.stride(1) != 1 or t.dtype != q.dtype:
+            raise KernelError(f"lightning: {name} must be [n, {width}] with a contiguous last dimension, of one dtype")
+    if out.dtype != torch.float32 or out.shape != (n, heads * dv) or out.stride(1) != 1:
+        raise KernelError("lightning: out must be float32 [n, heads * dv]")
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, dk, dv) or not state.is_contiguous():
+        raise KernelError(f"lightning: the state must be contiguous float32 [slots, {heads}, {dk}, {dv}]")
+    if decay.dtype != torch.float32 or decay.shape != (heads,) or not decay.is_contiguous():
+        raise KernelError("lightning: one float32 decay per head")
+    f = _func("lightning.cu", "lmsf_lightning_scan",
+              [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
+               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    rc = f(_ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(out), out.stride(0), _ptr(state),
+           _ptr(decay), _i32(cu_q, "cu_q"), _i32(state_slot, "state_slot"), n_seqs, heads, dk, dv, LIGHTNING_ACTS[act],
+           dtype_code(q.dtype), _stream())
+    _check(rc, "lightning.cu", "lmsf_lightning")
+
+
+def gated_norm(out: torch.Tensor, x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float):
+    """out = norm(x) * w * sigmoid(gate), the norm over a whole row, float32 inside.  x: float32 [n, width];
+    gate: [n, width] view of the activation type; out: contiguous, of the activation type."""
+    n, width = x.shape
+    if x.dtype != torch.float32 or x.stride(1) != 1 or gate.shape != x.shape or gate.stride(1) != 1 or \
+            out.shape != x.shape or not out.is_contiguous() or out.dtype != gate.dtype:
+        raise KernelError("gated_norm: x float32 [n, width], gate and out [n, width] of the activation type")
+    f = _func("lightning.cu", "lmsf_gated_norm",
+              [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    rc = f(_ptr(out), _ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _f32vec(w, width, "w"), n, width, float(eps),
+           dtype_code(out.dtype), _stream())
+    _check(rc, "lightning.cu", "lmsf_lightning")
+
+
+# ----------------------------------------------------------------------------- attention over a cached low-rank vector
+
+def latent_norm_cache_write(x: torch.Tensor, w: torch.Tensor, eps: float, cache: torch.Tensor, positions: torch.Tensor,
+                            token_seq: torch.Tensor, block_table: torch.Tensor, block_size: int, rank: int,
+                            error_flag: Optional[torch.Tensor] = None):
+    """cache[page of token t][slot] = norm(x[t]) * w, zero-padded to the cache's width.
+    x: [n, rank] view (last dimension contiguous); cache: [pages, 1, 1, block_size, padded rank]."""
+    n = x.shape[0]
+    padded = cache.shape[-1]
+    if x.shape != (n, rank) or x.stride(1) != 1 or cache.dtype != x.dtype or not cache.is_contiguous() or \
+            tuple(cache.shape[1:]) != (1, 1, block_size, padded) or padded < rank:
+        raise KernelError(f"latent cache: x [n, {rank}] and a cache [pages, 1, 1, {block_size}, >= {rank}] of one dtype")
+    f = _func("latent_cache.cu", "lmsf_latent_norm_cache_write",
+              [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+               c_int, c_float, c_int, c_void_p, c_void_p])
+    rc = f(_ptr(x), x.stride(0), _f32vec(w, rank, "w"), _ptr(cache), cache.stride(0), _i32(positions, "positions"),
+           _i32(token_seq, "token_seq"), _i32(block_table, "block_table"), block_table.shape[1], block_size, n, rank, padded,
+           float(eps), dtype_code(x.dtype), _i32(error_flag, "error_flag"), _stream())
+    _check(rc, "latent_cache.cu", "lmsf_latent_cache")
+
+
+def attention_shared_kv(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, block_size: int,
+                        token_seq: torch.Tensor, positions: torch.Tensor, scale: float, window: int, n_q_heads: int,
+                        head_dim: int, gate: Optional[torch.Tensor] = None):
+    """Attention of n_q_heads query heads over ONE cached vector per token that is key and value at once
+    (cache [pages, 1, 1, block_size, head_dim]); out[t, h] = sigmoid(gate[t, h]) * softmax(scale q K^T) K when a gate
+    ([n, n_q_heads] view) is given.  The plain kernel: any mix of tokens, fixed summation order."""
+    n = q.shape[0]
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_q_heads * head_dim or out.shape != q.shape:
+        raise KernelError("attention: q and out must be [n, heads * head_dim] with a contiguous last dimension")
+    if cache.dtype != q.dtype or out.dtype != q.dtype or not cache.is_contiguous() or \
+            tuple(cache.shape[1:]) != (1, 1, block_size, head_dim):
+        raise KernelError(f"attention: cache of shape {tuple(cache.shape)} / {cache.dtype} is not [pages, 1, 1, {block_size}, {head_dim}]")
+    if gate is not None and (gate.shape != (n, n_q_heads) or gate.stride(1) != 1 or gate.dtype != q.dtype):
+        raise KernelError("attention: the gate must be [n, heads] of q's dtype")
+    f = _func("attention_generic.cu", "lmsf_attention_generic_ext",
+              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
+               c_void_p, c_float, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_longlong,
+               c_void_p])
+    rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0),
+           _i32(block_table, "block_table"), block_table.shape[1], block_size, _i32(token_seq, "token_seq"),
+           _i32(positions, "positions"), float(scale), 0.0, None, int(window or 0), n, n_q_heads, 1, head_dim,
+           dtype_code(q.dtype), 1, _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
+    _check(rc, "attention_generic.cu", "lmsf_attention_generic")
+
+
+def gemm_tn_simt_batched(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor):
+    """out[:, b, :] = a[:, b, :] w[b]^T for every b.  a: [M, B, K], out: [M, B, N] (views: the last dimension
+    contiguous, any row and batch strides); w: [B, N, K].  float32 FMA accumulation in ascending k."""
+    M, B, K = a.shape
+    N = w.shape[1]
+    if w.shape != (B, N, K) or out.shape != (M, B, N) or a.stride(2) != 1 or w.stride(2) != 1 or out.stride(2) != 1 \
+            or a.dtype != w.dtype:
+        raise KernelError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    f = _func("gemm_simt.cu", "lmsf_gemm_tn_simt_batched",
+              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_longlong,
+               c_longlong, c_longlong, c_int, c_int, c_void_p])
+    rc = f(_ptr(out), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(1), out.stride(0), B, a.stride(1), w.stride(0),
+           out.stride(1), dtype_code(a.dtype), dtype_code(out.dtype), _stream())
+    _check(rc, "gemm_simt.cu", "lmsf_gemm_simt")
+
+
+# ----------------------------------------------------------------------------- routed experts
+
+MOE_ACTS = {None: 0, "none": 0, "relu2": 1}
+_MOE_TILE_ROWS: Optional[int] = None
+
+
+def moe_tile_rows() -> int:
+    global _MOE_TILE_ROWS
+    if _MOE_TILE_ROWS is None:
+        lib = load_library("moe.cu")
+        lib.lmsf_moe_tile_rows.restype = c_int
+        _MOE_TILE_ROWS = int(lib.lmsf_moe_tile_rows())
+    return _MOE_TILE_ROWS
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    """An upper bound of the row tiles of `pairs` (token, choice) pairs over `experts` experts, whatever the routing."""
+    return (pairs + moe_tile_rows() - 1) // moe_tile_rows() + min(experts, pairs)
+
+
+def moe_topk(ids: torch.Tensor, wts: torch.Tensor, logits: torch.Tensor, bias: Optional[torch.Tensor], experts: int):
+    """ids, wts [n, top]: the `top` largest of logits[t, :experts] + bias and the softmax over those alone."""
+    n, top = ids.shape
+    if logits.dtype != torch.float32 or logits.shape[0] != n or logits.shape[1] < experts or logits.stride(1) != 1:
+        raise KernelError("moe: the router's logits must be float32 [n, >= experts]")
+    if wts.dtype != torch.float32 or wts.shape != ids.shape or not wts.is_contiguous():
+        raise KernelError("moe: one float32 weight per choice")
+    f = _func("moe.cu", "lmsf_moe_topk", [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    rc = f(_ptr(logits), logits.stride(0), _f32vec(bias, experts, "bias"), n, experts, top, _i32(ids, "ids"), _ptr(wts), _stream())
+    _check(rc, "moe.cu", "lmsf_moe")
+
+
+def moe_align(ids: torch.Tensor, experts: int, offsets: torch.Tensor, pair_row: torch.Tensor, row_token: torch.Tensor,
+              tiles: torch.Tensor, meta: torch.Tensor):
+    """Sorts the (token, choice) pairs by expert on the device: offsets [experts + 1], pair_row [n, top] (row of each
+    pair in expert order), row_token [pairs], tiles [max_tiles, 4] and meta[0] = number of tiles."""
+    n, top = ids.shape
+    f = _func("moe.cu", "lmsf_moe_align",
+              [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    rc = f(_i32(ids, "ids"), n * top, top, experts, _i32(offsets, "offsets"), _i32(pair_row, "pair_row"),
+           _i32(row_token, "row_token"), _i32(tiles, "tiles"), tiles.shape[0], _i32(meta, "meta"), _stream())
+    _check(rc, "moe.cu", "lmsf_moe")
+
+
+def moe_grouped(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gather: Optional[torch.Tensor], tiles: torch.Tensor,
+                meta: torch.Tensor, act: Optional[str] = None):
+    """out[row] = act(a[gather[row] or row] w[expert of row]^T) for every row of the tile list.  w: [experts, N, K]."""
+    E, N, K = w.shape
+    if a.shape[1] != K or a.stride(1) != 1 or out.shape[1] != N or out.stride(1) != 1 or a.dtype != w.dtype or not w.is_contiguous():
+        raise KernelError(f"moe: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)}")
+    f = _func("moe.cu", "lmsf_moe_grouped",
+              [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
+               c_int, c_int, c_void_p])
+    rc = f(_ptr(out), _ptr(a), _ptr(w), _i32(gather, "gather"), _i32(tiles, "tiles"), _i32(meta, "meta"), tiles.shape[0], N, K,
+           a.stride(0), out.stride(0), MOE_ACTS[act], dtype_code(a.dtype), dtype_code(out.dtype), _stream())
+    _check(rc, "moe.cu", "lmsf_moe")
+
+
+def moe_combine(out: torch.Tensor, down: torch.Tensor, pair_row: torch.Tensor, wts: torch.Tensor,
+                shared: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None):
+    """out[t] = sum_j wts[t, j] * down[pair_row[t, j]] + sigmoid(gate[t]) * shared[t].  down: float32 [pairs, width];
+    gate: float32 [n] view (any stride); shared: [n, width] of out's dtype."""
+    n, width = out.shape
+    top = wts.shape[1]
+    if down.dtype != torch.float32 or down.shape[1] != width or not down.is_contiguous() or not out.is_contiguous():
+        raise KernelError("moe: down must be contiguous float32 [pairs, width] and out contiguous [n, width]")
+    if shared is not None and (shared.shape != out.shape or shared.dtype != out.dtype or not shared.is_contiguous()):
+        raise KernelError("moe: the shared expert's output must be like out")
+    if gate is not None and (gate.dtype != torch.float32 or gate.dim() != 1 or gate.shape[0] != n):
+        raise KernelError("moe: one float32 gate value per token")
+    f = _func("moe.cu", "lmsf_moe_combine",
+              [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
+    rc = f(_ptr(out), _ptr(down), _i32(pair_row, "pair_row"), _ptr(wts), top, _ptr(shared), _ptr(gate),
+           gate.stride(0) if gate is not None else 0, n, width, dtype_code(out.dtype), _stream())
+    _check(rc, "moe.cu", "lmsf_moe")
+
+
+def relu2_(x: torch.Tensor):
+    """x <- max(x, 0)^2 in place."""
+    if not x.is_contiguous():
+        raise KernelError("relu2: x must be contiguous")
+    f = _func("moe.cu", "lmsf_relu2", [c_void_p, c_longlong, c_int, c_void_p])
+    rc = f(_ptr(x), x.numel(), dtype_code(x.dtype), _stream())
+    _check(rc, "moe.cu", "lmsf_moe")

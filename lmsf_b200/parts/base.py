@@ -41,9 +41,13 @@ class LayerSpec:
 @dataclass
 class LayerCall:
     """One entry of the run order.  `layer` indexes ModelSpec.layers.  `cache_of`: index of an
-    EARLIER entry of the order whose cache this call reads instead of owning one."""
+    EARLIER entry of the order whose cache this call reads instead of owning one.  `entry`: index into
+    ModelSpec.entries of a part that changes the residual stream right before this call (what a repeated span of
+    layers adds at the start of each pass); `entry_pass` is the number of the pass that starts here."""
     layer: int
     cache_of: Optional[int] = None
+    entry: Optional[int] = None
+    entry_pass: int = 0
 
 
 @dataclass
@@ -58,6 +62,7 @@ class ModelSpec:
     lm_head: PartSpec
     eos_token_ids: List[int] = field(default_factory=list)
     ignored_weights: List[str] = field(default_factory=list)     # regular expressions of tensors to skip
+    entries: List[PartSpec] = field(default_factory=list)        # family "stream_entry", named by LayerCall.entry
 
 
 @dataclass
@@ -70,11 +75,13 @@ class WeightSpec:
 
 @dataclass(frozen=True)
 class KVCacheSpec:
-    """What a mixer needs of the paged cache: per token and layer 2 * num_kv_heads * head_dim
-    values; window None keeps all keys, window w keeps the last w."""
+    """What a mixer needs of the paged cache: per token and layer planes * num_kv_heads * head_dim
+    values; window None keeps all keys, window w keeps the last w.  planes 2: keys and values; planes 1: one vector
+    per token and kv head that serves as both (attention over a cached low-rank vector)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -97,7 +104,7 @@ class CacheGroupView:
 @dataclass
 class LayerCache:
     """The cache of one call of the order, as its mixer sees it."""
-    kv: Optional[torch.Tensor] = None          # [pages, 2, kv_heads, block_size, head_dim]
+    kv: Optional[torch.Tensor] = None          # [pages, planes, kv_heads, block_size, head_dim]
     group: Optional[int] = None                # index into StepContext.groups
     state: Optional[torch.Tensor] = None       # [slots, *StateSpec.shape]
     owner: bool = True                         # False: read another call's cache, write nothing
@@ -213,6 +220,24 @@ class Prenormed:
     res: torch.Tensor
 
 
+@dataclass
+class Normed:
+    """The residual stream `res` holds every branch so far and `h` is already `norm` of it: what a block returns as
+    x when it has applied the next block's first norm itself (or None as x: nothing is pending, no norm applied)."""
+    h: torch.Tensor
+    norm: Norm
+    res: torch.Tensor
+
+
+class StreamEntry(Part):
+    """Changes the float32 residual stream in place before a call of the order: `forward(ctx, res, first, n_pass)`,
+    where `first` is the stream as the embedding left it."""
+    needs_first = False     # True: the model keeps a copy of the embedding's output for it
+
+    def forward(self, ctx: "StepContext", res: torch.Tensor, first: Optional[torch.Tensor], n_pass: int) -> None:
+        raise NotImplementedError
+
+
 class PositionEncoding(Part):
     def apply(self, ctx: StepContext, q: torch.Tensor, k: Optional[torch.Tensor], n_q_heads: int, n_kv_heads: int,
               head_dim: int) -> None:
@@ -258,6 +283,7 @@ class Block:
     """An arrangement of parts.  `parts` maps role names to built parts; the block says which
     roles it needs in `ROLES` (role -> family)."""
     ROLES: Dict[str, str] = {}
+    OPTIONAL_ROLES: Tuple[str, ...] = ()     # roles of ROLES that a layer may leave out
 
     def __init__(self, parts: Dict[str, Part], **params):
         self.parts = parts
@@ -282,7 +308,7 @@ class Block:
 
 # ----------------------------------------------------------------------------- registries
 
-FAMILIES = ("mixer", "feed_forward", "norm", "position_encoding", "block", "embedding", "linear")
+FAMILIES = ("mixer", "feed_forward", "norm", "position_encoding", "block", "embedding", "linear", "stream_entry")
 _REGISTRY: Dict[str, Dict[str, Callable[..., Any]]] = {f: {} for f in FAMILIES}
 
 

@@ -12,7 +12,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from .. import kernels
-from .base import Block, LayerCache, Norm, NormAfter, Part, StepContext, register_part
+from .base import Block, LayerCache, Norm, NormAfter, Normed, Part, StepContext, register_part
 
 # A step of a few tokens in bfloat16: a norm between two weight-streaming products is done by those products
 # (the one before adds to the residual stream and leaves sums of squares, the one after divides).  LMSF_FUSE_NORMS=0:
@@ -52,3 +52,54 @@ class PreNormBlock(Block):
         then = norm_after(ctx, self.feed_forward, next_entry[0], next_entry[1], res) if next_entry is not None else None
         out = self.feed_forward.forward(ctx, h, then=then) if then is not None else self.feed_forward.forward(ctx, h)
         return out, res
+
+
+@register_part("block", "sandwich_norm")
+class SandwichNormBlock(Block):
+    """A norm before AND after each branch:  x <- x + post(mixer(pre(x))),  x <- x + post(ff(pre(x))), where a post norm
+    may carry a layer scale (a learned vector that multiplies its output).  The residual stream is float32 and every
+    sum into it is made in float32 from the float32 normed branch (the branch is never rounded before it is added).
+    One kernel does what lies between two branches: the post norm of the branch before, the add, and the pre norm of
+    the branch after (`kernels.stream_norm`); with `next_entry` it also applies the next block's first norm and
+    hands it over as a `Normed`.  A layer may have no feed-forward."""
+    ROLES = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm",
+             "ffn_norm": "norm", "feed_forward": "feed_forward", "ffn_post_norm": "norm"}
+    OPTIONAL_ROLES = ("ffn_norm", "feed_forward", "ffn_post_norm")
+    fuses_next_norm = True
+
+    def __init__(self, parts: Dict[str, Part]):
+        super().__init__(parts)
+        self.mixer_norm, self._mixer, self.mixer_post = parts["mixer_norm"], parts["mixer"], parts["mixer_post_norm"]
+        self.feed_forward = parts.get("feed_forward")
+        self.ffn_norm, self.ffn_post = parts.get("ffn_norm"), parts.get("ffn_post_norm")
+        if self.feed_forward is not None and (self.ffn_norm is None or self.ffn_post is None):
+            raise ValueError("a feed-forward needs the norms before and after it")
+        for n in (self.mixer_norm, self.mixer_post, self.ffn_norm, self.ffn_post):
+            if n is not None and not hasattr(n, "weight_f32"):
+                raise ValueError("the sandwich block takes norms that are a factor per row times a weight (rmsnorm)")
+
+    def entry(self) -> Optional[Tuple[Norm, Part]]:
+        return self.mixer_norm, self._mixer
+
+    @staticmethod
+    def _between(res: torch.Tensor, branch: torch.Tensor, post, nxt: Optional[Norm]):
+        """res += post(branch); returns nxt(res) in the branch's type (None without nxt)."""
+        h = torch.empty_like(branch) if nxt is not None else None
+        kernels.stream_norm(res, y=branch, w_post=post.weight_f32(), layer_scale=post.scale_f32(), eps_post=post.eps,
+                            h=h, w_next=nxt.weight_f32() if nxt is not None else None,
+                            eps_next=nxt.eps if nxt is not None else 0.0)
+        return h
+
+    def forward(self, ctx: StepContext, x, res: Optional[torch.Tensor], cache: LayerCache,
+                next_entry: Optional[Tuple[Norm, Part]] = None):
+        h, res = self.mixer_norm.forward_residual(x, res)      # x: None (complete stream), a Normed, or a pending branch
+        a = self._mixer.forward(ctx, h, cache)
+        nxt = next_entry[0] if next_entry is not None and hasattr(next_entry[0], "weight_f32") and \
+            not getattr(next_entry[0], "has_layer_scale", False) else None
+        if self.feed_forward is None:
+            h = self._between(res, a, self.mixer_post, nxt)
+            return (Normed(h, nxt, res) if nxt is not None else None), res
+        h = self._between(res, a, self.mixer_post, self.ffn_norm)
+        f = self.feed_forward.forward(ctx, h)
+        h = self._between(res, f, self.ffn_post, nxt)
+        return (Normed(h, nxt, res) if nxt is not None else None), res

@@ -25,26 +25,35 @@ class DecoderModel:
         self._owned: List[Tuple[Part, PartSpec]] = list(with_nested(self.embedding, spec.embedding))
         for ls in spec.layers:
             cls = part_class("block", ls.block)
-            missing = [r for r in cls.ROLES if r not in ls.parts]
+            missing = [r for r in cls.ROLES if r not in ls.parts and r not in cls.OPTIONAL_ROLES]
             if missing:
                 raise ValueError(f"block {ls.block!r} needs the parts {sorted(cls.ROLES)}; missing {missing}")
             parts = {}
             for role, family in cls.ROLES.items():
+                if role not in ls.parts:
+                    continue
                 parts[role] = build_part(family, ls.parts[role])
                 self._owned += list(with_nested(parts[role], ls.parts[role]))
             self.blocks.append(cls(parts, **ls.block_params))
         self.final_norm = build_part("norm", spec.final_norm)
         self.lm_head = build_part("linear", spec.lm_head)
         self._owned += [*with_nested(self.final_norm, spec.final_norm), *with_nested(self.lm_head, spec.lm_head)]
+        self.entries = [build_part("stream_entry", es) for es in spec.entries]
+        for part, es in zip(self.entries, spec.entries):
+            self._owned += list(with_nested(part, es))
         self.calls = list(spec.order)
+        # debugging aid: called as layer_hook(j, x, res) after call j of the order with what the block returned
+        self.layer_hook = None
         for j, call in enumerate(self.calls):
             if not (0 <= call.layer < len(self.blocks)):
                 raise ValueError(f"order[{j}] names layer {call.layer}, the model has {len(self.blocks)}")
+            if call.entry is not None and not (0 <= call.entry < len(self.entries)):
+                raise ValueError(f"order[{j}] names entry {call.entry}, the model has {len(self.entries)}")
             if call.cache_of is not None:
                 if not (0 <= call.cache_of < j) or self.calls[call.cache_of].cache_of is not None:
                     raise ValueError(f"order[{j}].cache_of must name an earlier entry that owns its cache")
                 a, b = self.call_cache_spec(j), self.call_cache_spec(call.cache_of)
-                if a is None or b is None or (a.num_kv_heads, a.head_dim) != (b.num_kv_heads, b.head_dim):
+                if a is None or b is None or (a.num_kv_heads, a.head_dim, a.planes) != (b.num_kv_heads, b.head_dim, b.planes):
                     raise ValueError(f"order[{j}] cannot read the cache of order[{call.cache_of}]: "
                                      f"their key/value shapes differ")
 
@@ -67,20 +76,41 @@ class DecoderModel:
     # ---- the forward pass of one step
     def forward(self, ctx: StepContext, caches: List[LayerCache], logit_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """logits float32 [len(logit_rows), vocab]; logit_rows: int32 indices into the step's tokens."""
-        x = self.embedding.forward(ctx)
-        res = None
+        res = first = None
+        if getattr(self.embedding, "emits_stream", False):
+            # the embedding leaves the float32 residual stream itself (nothing pending); a copy is kept when a later
+            # entry of the order adds it again
+            keep = any(c.entry is not None and self.entries[c.entry].needs_first for c in self.calls)
+            res, first = self.embedding.forward_stream(ctx, keep)
+            x = None
+        else:
+            x = self.embedding.forward(ctx)
         for j, call in enumerate(self.calls):
             block = self.blocks[call.layer]
+            if call.entry is not None:
+                if res is None or x is not None:
+                    raise ValueError("a stream entry needs a block before it (or an embedding) that leaves nothing pending")
+                self.entries[call.entry].forward(ctx, res, first, call.entry_pass)
             # a block that can take the next block's first norm into its last product is told that norm and its reader
-            entry = self.blocks[self.calls[j + 1].layer].entry() if block.fuses_next_norm and j + 1 < len(self.calls) else None
+            # (not across an entry that changes the stream in between)
+            entry = None
+            if block.fuses_next_norm and j + 1 < len(self.calls) and self.calls[j + 1].entry is None:
+                entry = self.blocks[self.calls[j + 1].layer].entry()
             with span(f"layer {call.layer}"):
                 if entry is not None:
                     x, res = block.forward(ctx, x, res, caches[j], next_entry=entry)
                 else:
                     x, res = block.forward(ctx, x, res, caches[j])
+            if self.layer_hook is not None:
+                self.layer_hook(j, x, res)
         n_rows = 0 if logit_rows is None else logit_rows.numel()
         if n_rows == 0:
-            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)
+        if x is None:                                             # nothing pending: the stream is complete
+            rs = torch.empty((n_rows, res.shape[1]), dtype=res.dtype, device=res.device)
+            kernels.embedding(rs, res, logit_rows)                # a row gather
+            h, _ = self.final_norm.forward_residual(None, rs)
+            return self.lm_head.forward(h)
         xs = torch.empty((n_rows, x.shape[1]), dtype=x.dtype, device=x.device)
         kernels.embedding(xs, x, logit_rows)                     # a row gather
         if res is None:

@@ -25,3 +25,33 @@ class TokenEmbedding(Part):
         x = torch.empty((ctx.n_tokens, self.hidden_size), dtype=self.weight.dtype, device=self.weight.device)
         kernels.embedding(x, self.weight, ctx.token_ids, ctx.error_flag, scale=self.scale)
         return x
+
+
+@register_part("embedding", "normed_token_embedding")
+class NormedTokenEmbedding(Part):
+    """x[t] = norm(E[id_t] * scale) * w: an embedding that passes through an RMS norm before it enters the residual
+    stream.  The norm is float32 and its output IS the float32 stream (`emits_stream`): nothing is rounded in between.
+    One kernel gathers, norms and, when asked, leaves a second copy of the result for layers that add it again."""
+    graph_safe = True
+    emits_stream = True
+
+    def __init__(self, vocab_size: int, hidden_size: int, eps: float, scale: float = 1.0):
+        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.eps, self.scale = float(eps), float(scale)
+        self.weight: Optional[torch.Tensor] = None
+        self.norm: Optional[torch.Tensor] = None
+        self._norm32: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {"weight": WeightSpec([(self.vocab_size, self.hidden_size)]),
+                "norm": WeightSpec([(self.hidden_size,)], keep_fp32=True)}
+
+    def prepare(self, dtype, device) -> None:
+        self._norm32 = self.norm.float().contiguous()
+
+    def forward_stream(self, ctx: StepContext, keep: bool = False):
+        """(stream, copy of it or None), both float32 [n_tokens, hidden]."""
+        res = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=self.weight.device)
+        first = torch.empty_like(res) if keep else None
+        kernels.embed_norm(res, first, self.weight, ctx.token_ids, self._norm32, self.eps, self.scale, ctx.error_flag)
+        return res, first

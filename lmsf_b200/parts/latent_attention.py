@@ -1,0 +1,92 @@
+"""Attention whose keys and values are expanded from one low-rank vector per token, which is all that is cached.
+
+  q = h Wq^T [heads x dk];  c = norm(h Wd^T) * w [rank];  k = c Wuk^T, v = c Wuv^T per head
+  out = (sigmoid(h Wg^T)_head * softmax(scale q k^T over the window) v) Wo^T        (no position encoding)
+
+Keys and values are linear in c, so the attention runs on c itself: the key expansion moves into the query
+(q' = q Wuk per head, rank values), every head attends over the same cached c as key AND value (one kv head, one
+plane of the paged cache: `KVCacheSpec(planes=1)`), and the value expansion is applied to the attention's output.
+A step costs two small batched products per token instead of expanding every cached token again, and a page holds
+`rank` values per token instead of heads x (dk + dv).  The rank is padded with zeros to what the attention kernels
+take (a multiple of 16).  The norm of c is fused with the cache write (csrc/latent_cache.cu); the gate is applied by
+the attention kernel to its output (it commutes with the linear value expansion).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import kernels
+from .base import KVCacheSpec, LayerCache, Mixer, StepContext, WeightSpec, register_part
+from .linear import batched_matmul_tn, matmul_tn
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, value_dim: int, kv_rank: int, eps: float,
+                 scale: Optional[float] = None, window: Optional[int] = None, gate: bool = True):
+        self.hidden_size, self.num_heads, self.head_dim, self.value_dim = int(hidden_size), int(num_heads), int(head_dim), int(value_dim)
+        self.kv_rank = int(kv_rank)
+        self.padded_rank = (self.kv_rank + 15) // 16 * 16
+        if self.padded_rank > 256:
+            raise ValueError(f"kv_rank {kv_rank} is beyond the attention kernels (up to 256)")
+        self.eps = float(eps)
+        self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
+        self.window = int(window) if window else None
+        self.has_gate = bool(gate)
+        self.q_size, self.v_size = self.num_heads * self.head_dim, self.num_heads * self.value_dim
+        self.qcg: Optional[torch.Tensor] = None
+        self.c_norm: Optional[torch.Tensor] = None
+        self.uk: Optional[torch.Tensor] = None
+        self.uv: Optional[torch.Tensor] = None
+        self.o: Optional[torch.Tensor] = None
+        self._uk_t: Optional[torch.Tensor] = None
+        self._uv3: Optional[torch.Tensor] = None
+        self._norm32: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        D, R = self.hidden_size, self.kv_rank
+        merged = [(self.q_size, D), (R, D)] + ([(self.num_heads, D)] if self.has_gate else [])
+        return {"qcg": WeightSpec(merged), "c_norm": WeightSpec([(R,)], keep_fp32=True),
+                "uk": WeightSpec([(self.q_size, R)]), "uv": WeightSpec([(self.v_size, R)]),
+                "o": WeightSpec([(D, self.v_size)])}
+
+    def cache_spec(self) -> Optional[KVCacheSpec]:
+        return KVCacheSpec(1, self.padded_rank, self.window, planes=1)
+
+    def activation_width(self) -> int:
+        return self.q_size + self.kv_rank + self.num_heads + 2 * self.num_heads * self.padded_rank + self.v_size
+
+    def prepare(self, dtype, device) -> None:
+        H, dk, dv, R, Rp = self.num_heads, self.head_dim, self.value_dim, self.kv_rank, self.padded_rank
+        # the key expansion as the query sees it: per head [rank (padded with zero rows), dk]
+        uk_t = torch.zeros((H, Rp, dk), dtype=self.uk.dtype, device=self.uk.device)
+        uk_t[:, :R, :] = self.uk.view(H, dk, R).transpose(1, 2)
+        self._uk_t = uk_t
+        self._uv3 = self.uv.view(H, dv, R)
+        self._norm32 = self.c_norm.float().contiguous()
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
+        H, dk, dv, R, Rp = self.num_heads, self.head_dim, self.value_dim, self.kv_rank, self.padded_rank
+        n = ctx.n_tokens
+        group = ctx.groups[cache.group]
+        p = matmul_tn(h, self.qcg)
+        q, c_raw = p[:, :self.q_size], p[:, self.q_size:self.q_size + R]
+        g = p[:, self.q_size + R:] if self.has_gate else None
+        if cache.owner:
+            kernels.latent_norm_cache_write(c_raw, self._norm32, self.eps, cache.kv, ctx.positions, ctx.token_seq,
+                                            group.block_table, group.block_size, R, ctx.error_flag)
+        qa = torch.empty((n, H * Rp), dtype=p.dtype, device=p.device)
+        batched_matmul_tn(qa.view(n, H, Rp), q.view(n, H, dk), self._uk_t)
+        oa = torch.empty_like(qa)
+        self.attend(ctx, oa, qa, cache.kv, group, g)
+        out = torch.empty((n, self.v_size), dtype=p.dtype, device=p.device)
+        batched_matmul_tn(out.view(n, H, dv), oa.view(n, H, Rp)[:, :, :R], self._uv3)
+        return matmul_tn(out, self.o)
+
+    def attend(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group, gate) -> None:
+        kernels.attention_shared_kv(out, q, kv, group.block_table, group.block_size, ctx.token_seq, ctx.positions,
+                                    self.scale, self.window or 0, self.num_heads, self.padded_rank, gate=gate)

@@ -77,6 +77,18 @@ def _product_tn(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtyp
     return out
 
 
+def batched_matmul_tn(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """out[:, b, :] = a[:, b, :] w[b]^T for every b: one product per head of an activation matrix.
+    a: [M, B, K] and out: [M, B, N] are views with a contiguous last dimension; w: [B, N, K].
+    bfloat16 with more than 16 rows: the library's batched product; else this package's FFMA kernel (true 32-bit
+    for float32; few rows in bfloat16, where the product is a stream over w)."""
+    if a.dtype == torch.bfloat16 and a.shape[0] > kernels.SKINNY_MAX_M:
+        torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+    else:
+        kernels.gemm_tn_simt_batched(out, a, w)
+    return out
+
+
 def matmul_tn_residual(x: torch.Tensor, w: torch.Tensor, then: NormAfter) -> Optional[Prenormed]:
     """The product before a norm, for a few rows: then.res += x w^T, and the first half of then.norm on the new
     residual.  None when this product cannot do it (the caller then multiplies as usual and the norm runs whole)."""

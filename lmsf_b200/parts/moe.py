@@ -1,0 +1,89 @@
+"""Routed experts: `experts` small feed-forward layers of which every token uses `top`, plus an optional shared expert.
+
+  z = h Wr^T + b (float32);  the `top` largest z are chosen, their weights are the softmax over the chosen z alone
+  out = sum_j weight_j * expert_(e_j)(h)  +  sigmoid(h ws^T) * shared(h)
+  expert(h) = act(h Wup^T) Wdown^T,  act = the square of relu (no gate matrix, no biases)
+
+All experts' matrices are stacked ([experts, ff, width], [experts, width, ff]).  The routing is sorted on the device
+(csrc/moe.cu): no value comes back to the host, and a step's launches have the same shape whatever the routing is, so
+decode steps can be replayed from CUDA graphs.  The router and the shared expert's gate are rows of one float32 product.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import kernels
+from .base import FeedForward, StepContext, WeightSpec, register_part
+from .linear import matmul_tn
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_experts: int, top_k: int, expert_size: int, shared_size: int = 0,
+                 activation: str = "relu2", router_bias: bool = True, shared_gate: bool = True):
+        if not (0 < top_k <= num_experts):
+            raise ValueError(f"{top_k} choices of {num_experts} experts")
+        if activation not in kernels.MOE_ACTS:
+            raise ValueError(f"activation {activation!r} is not supported (known: relu2, none)")
+        self.hidden_size, self.num_experts, self.top_k = int(hidden_size), int(num_experts), int(top_k)
+        self.expert_size, self.shared_size = int(expert_size), int(shared_size or 0)
+        self.activation = activation
+        self.has_router_bias = bool(router_bias)
+        self.has_shared_gate = bool(shared_gate) and self.shared_size > 0
+        self.up: Optional[torch.Tensor] = None
+        self.down: Optional[torch.Tensor] = None
+        self.router: Optional[torch.Tensor] = None
+        self.router_bias: Optional[torch.Tensor] = None
+        self.shared_up: Optional[torch.Tensor] = None
+        self.shared_down: Optional[torch.Tensor] = None
+        self._bias32: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        D, E, F = self.hidden_size, self.num_experts, self.expert_size
+        specs = {"up": WeightSpec([(F, D)] * E), "down": WeightSpec([(D, F)] * E),
+                 "router": WeightSpec([(E, D)] + ([(1, D)] if self.has_shared_gate else []))}
+        if self.has_router_bias:
+            specs["router_bias"] = WeightSpec([(E,)], keep_fp32=True)
+        if self.shared_size:
+            specs["shared_up"] = WeightSpec([(self.shared_size, D)])
+            specs["shared_down"] = WeightSpec([(D, self.shared_size)])
+        return specs
+
+    def activation_width(self) -> int:
+        return self.top_k * (self.expert_size + 2 * self.hidden_size) + self.shared_size + self.hidden_size
+
+    def prepare(self, dtype, device) -> None:
+        self._bias32 = self.router_bias.float().contiguous() if self.has_router_bias else None
+
+    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        n, D, E, K, F = h.shape[0], self.hidden_size, self.num_experts, self.top_k, self.expert_size
+        dev = h.device
+        z = matmul_tn(h, self.router, out_dtype=torch.float32)           # [n, experts (+ 1: the shared expert's gate)]
+        ids = torch.empty((n, K), dtype=torch.int32, device=dev)
+        wts = torch.empty((n, K), dtype=torch.float32, device=dev)
+        kernels.moe_topk(ids, wts, z, self._bias32, E)
+        pairs = n * K
+        max_tiles = kernels.moe_max_tiles(pairs, E)
+        book = torch.empty(E + 1 + 2 * pairs + 4 * max_tiles + 4, dtype=torch.int32, device=dev)
+        offsets, pair_row = book[:E + 1], book[E + 1:E + 1 + pairs].view(n, K)
+        row_token = book[E + 1 + pairs:E + 1 + 2 * pairs]
+        tiles = book[E + 1 + 2 * pairs:E + 1 + 2 * pairs + 4 * max_tiles].view(max_tiles, 4)
+        meta = book[E + 1 + 2 * pairs + 4 * max_tiles:]
+        kernels.moe_align(ids, E, offsets, pair_row, row_token, tiles, meta)
+        y = torch.empty((pairs, F), dtype=h.dtype, device=dev)
+        kernels.moe_grouped(y, h, self.up.view(E, F, D), row_token, tiles, meta, act=self.activation)
+        d = torch.empty((pairs, D), dtype=torch.float32, device=dev)
+        kernels.moe_grouped(d, y, self.down.view(E, D, F), None, tiles, meta)
+        shared = None
+        if self.shared_size:
+            s = matmul_tn(h, self.shared_up)
+            if self.activation == "relu2":
+                kernels.relu2_(s)
+            shared = matmul_tn(s, self.shared_down)
+        out = torch.empty((n, D), dtype=h.dtype, device=dev)
+        kernels.moe_combine(out, d, pair_row, wts, shared, z[:, E] if self.has_shared_gate else None)
+        return out
