@@ -109,7 +109,8 @@ def layer(x, cfg, weights, i):
 
 
 def run_order(cfg):
-    """[(layer, pass number or None)]: the layers in the order they run; the looped span is repeated."""
+    """[(layer, pass number or None, whether a pass starts here)]: the layers in the order they run; the span that
+    runs several times is repeated."""
     n = len(cfg["layers"])
     loop = cfg.get("loop")
     if not loop or loop["times"] < 1 or loop["stop"] <= loop["start"]:

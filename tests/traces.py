@@ -200,7 +200,8 @@ def run_program(folder, dtype, steps, max_tokens, env=None):
         assert line == f"done {s['step']}", line
     proc.stdin.close()
     assert proc.wait(timeout=120) == 0
-    vocab = json.load(open(os.path.join(folder, "config.json")))["vocab_size"]
+    cfg = json.load(open(os.path.join(folder, "config.json")))
+    vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     outputs = {}
     for s in steps:
         p = os.path.join(out, f"{s['step']}.f32")
