@@ -216,13 +216,14 @@ LMSF_API int lmsf_moe_topk(const float* logits, long long ld, const float* bias,
 
 LMSF_API int lmsf_moe_tile_rows() { return lmsf::BM; }
 
-LMSF_API int lmsf_moe_align(const int* ids, int pairs, int top, int experts, int* offsets, int* pair_row, int* row_token,
-                            int* tiles, int max_tiles, int* meta, void* stream) {
+// tile_rows: rows per tile of the product that will walk the list (lmsf_moe_tile_rows() for the kernel of this file).
+LMSF_API int lmsf_moe_align(const int* ids, int pairs, int top, int experts, int tile_rows, int* offsets, int* pair_row,
+                            int* row_token, int* tiles, int max_tiles, int* meta, void* stream) {
   using namespace lmsf;
   if (pairs <= 0) return 0;
-  if (experts <= 0 || experts > kMaxExperts || top <= 0) LMSF_REFUSE("moe: experts=%d top=%d", experts, top);
-  if (max_tiles < ceil_div(pairs, BM) + min(experts, pairs)) LMSF_REFUSE("moe: room for %d tiles is too little", max_tiles);
-  moe_align_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(ids, pairs, top, experts, BM, offsets, pair_row, row_token, tiles,
+  if (experts <= 0 || experts > kMaxExperts || top <= 0 || tile_rows <= 0) LMSF_REFUSE("moe: experts=%d top=%d", experts, top);
+  if (max_tiles < pairs / tile_rows + min(experts, pairs)) LMSF_REFUSE("moe: room for %d tiles is too little", max_tiles);
+  moe_align_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(ids, pairs, top, experts, tile_rows, offsets, pair_row, row_token, tiles,
                                                          max_tiles, meta);
   return LMSF_LAUNCH_STATUS();
 }
@@ -233,6 +234,7 @@ LMSF_API int lmsf_moe_grouped(void* C, const void* A, const void* W, const int* 
                               void* stream) {
   using namespace lmsf;
   if (max_tiles <= 0 || N <= 0) return 0;
+  // (the tile list must have been made with tile_rows = lmsf_moe_tile_rows())
   if (K <= 0 || lda < K || ldc < N) LMSF_REFUSE("moe: N=%d K=%d lda=%lld ldc=%lld", N, K, lda, ldc);
   if (max_tiles > 65535) LMSF_REFUSE("moe: more than 65535 row tiles in one launch");
   if (act != 0 && act != 1) LMSF_REFUSE("moe: unknown activation code %d", act);

@@ -874,9 +874,31 @@ def moe_tile_rows() -> int:
     return _MOE_TILE_ROWS
 
 
-def moe_max_tiles(pairs: int, experts: int) -> int:
+MOE_TC_TILE_ROWS = 128      # rows per tile of the tensor-core product (csrc/moe_tc.cu)
+
+
+def moe_max_tiles(pairs: int, experts: int, tile_rows: int) -> int:
     """An upper bound of the row tiles of `pairs` (token, choice) pairs over `experts` experts, whatever the routing."""
-    return (pairs + moe_tile_rows() - 1) // moe_tile_rows() + min(experts, pairs)
+    return pairs // tile_rows + min(experts, pairs)
+
+
+def moe_grouped_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0
+            and a.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
+
+
+def moe_grouped_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gather: Optional[torch.Tensor], tiles: torch.Tensor,
+                   meta: torch.Tensor, act: Optional[str] = None, error_flag: Optional[torch.Tensor] = None):
+    """`moe_grouped` on the tensor cores (bfloat16 operands, tiles of MOE_TC_TILE_ROWS rows; out bfloat16 or float32)."""
+    E, N, K = w.shape
+    if not moe_grouped_tc_supported(a, w) or a.shape[1] != K or out.shape[1] != N or out.stride(1) != 1:
+        raise KernelError(f"moe_tc: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} are not taken")
+    f = _func("moe_tc.cu", "lmsf_moe_grouped_tc",
+              [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
+               c_int, c_void_p, c_void_p])
+    rc = f(_ptr(out), _ptr(a), _ptr(w), _i32(gather, "gather"), _i32(tiles, "tiles"), _i32(meta, "meta"), tiles.shape[0], N, K,
+           a.stride(0), out.stride(0), MOE_ACTS[act], dtype_code(out.dtype), _i32(error_flag, "error_flag"), _stream())
+    _check(rc, "moe_tc.cu", "lmsf_moe_tc")
 
 
 def moe_topk(ids: torch.Tensor, wts: torch.Tensor, logits: torch.Tensor, bias: Optional[torch.Tensor], experts: int):
@@ -891,14 +913,14 @@ def moe_topk(ids: torch.Tensor, wts: torch.Tensor, logits: torch.Tensor, bias: O
     _check(rc, "moe.cu", "lmsf_moe")
 
 
-def moe_align(ids: torch.Tensor, experts: int, offsets: torch.Tensor, pair_row: torch.Tensor, row_token: torch.Tensor,
-              tiles: torch.Tensor, meta: torch.Tensor):
+def moe_align(ids: torch.Tensor, experts: int, tile_rows: int, offsets: torch.Tensor, pair_row: torch.Tensor,
+              row_token: torch.Tensor, tiles: torch.Tensor, meta: torch.Tensor):
     """Sorts the (token, choice) pairs by expert on the device: offsets [experts + 1], pair_row [n, top] (row of each
     pair in expert order), row_token [pairs], tiles [max_tiles, 4] and meta[0] = number of tiles."""
     n, top = ids.shape
     f = _func("moe.cu", "lmsf_moe_align",
-              [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
-    rc = f(_i32(ids, "ids"), n * top, top, experts, _i32(offsets, "offsets"), _i32(pair_row, "pair_row"),
+              [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    rc = f(_i32(ids, "ids"), n * top, top, experts, int(tile_rows), _i32(offsets, "offsets"), _i32(pair_row, "pair_row"),
            _i32(row_token, "row_token"), _i32(tiles, "tiles"), tiles.shape[0], _i32(meta, "meta"), _stream())
     _check(rc, "moe.cu", "lmsf_moe")
 

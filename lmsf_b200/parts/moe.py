@@ -19,6 +19,9 @@ from .base import FeedForward, StepContext, WeightSpec, register_part
 from .linear import matmul_tn
 
 
+USE_TC = True      # bfloat16: the experts' products on tcgen05 (csrc/moe_tc.cu)
+
+
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(FeedForward):
     graph_safe = True
@@ -67,17 +70,27 @@ class RoutedExperts(FeedForward):
         wts = torch.empty((n, K), dtype=torch.float32, device=dev)
         kernels.moe_topk(ids, wts, z, self._bias32, E)
         pairs = n * K
-        max_tiles = kernels.moe_max_tiles(pairs, E)
+        up3, down3 = self.up.view(E, F, D), self.down.view(E, D, F)
+        # bfloat16: the experts' products run on the tensor cores (tiles of 128 rows); float32, or sizes that the
+        # 16-byte copies cannot take: the FFMA kernel (tiles of 64 rows)
+        use_tc = USE_TC and F % 8 == 0 and kernels.moe_grouped_tc_supported(h, up3) and down3.data_ptr() % 16 == 0
+        tile_rows = kernels.MOE_TC_TILE_ROWS if use_tc else kernels.moe_tile_rows()
+        max_tiles = kernels.moe_max_tiles(pairs, E, tile_rows)
         book = torch.empty(E + 1 + 2 * pairs + 4 * max_tiles + 4, dtype=torch.int32, device=dev)
         offsets, pair_row = book[:E + 1], book[E + 1:E + 1 + pairs].view(n, K)
         row_token = book[E + 1 + pairs:E + 1 + 2 * pairs]
         tiles = book[E + 1 + 2 * pairs:E + 1 + 2 * pairs + 4 * max_tiles].view(max_tiles, 4)
         meta = book[E + 1 + 2 * pairs + 4 * max_tiles:]
-        kernels.moe_align(ids, E, offsets, pair_row, row_token, tiles, meta)
+        kernels.moe_align(ids, E, tile_rows, offsets, pair_row, row_token, tiles, meta)
         y = torch.empty((pairs, F), dtype=h.dtype, device=dev)
-        kernels.moe_grouped(y, h, self.up.view(E, F, D), row_token, tiles, meta, act=self.activation)
         d = torch.empty((pairs, D), dtype=torch.float32, device=dev)
-        kernels.moe_grouped(d, y, self.down.view(E, D, F), None, tiles, meta)
+        if use_tc:
+            flag = ctx.error_flag if ctx is not None else None
+            kernels.moe_grouped_tc(y, h, up3, row_token, tiles, meta, act=self.activation, error_flag=flag)
+            kernels.moe_grouped_tc(d, y, down3, None, tiles, meta, error_flag=flag)
+        else:
+            kernels.moe_grouped(y, h, up3, row_token, tiles, meta, act=self.activation)
+            kernels.moe_grouped(d, y, down3, None, tiles, meta)
         shared = None
         if self.shared_size:
             s = matmul_tn(h, self.shared_up)
