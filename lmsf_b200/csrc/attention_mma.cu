@@ -585,7 +585,7 @@ LMSF_API int lmsf_attention_decode_width(const void* q, long long q_stride, void
                                          const int* block_table, int max_blocks, const int* seq_ids, int n_served,
                                          int n_seqs_total, const int* cu_q, const int* ctx_len, float scale, int window,
                                          int n_q_heads, int head_dim, int n_splits, int block_warps, void* scratch,
-                                         void* stream) {
+                                         int kv_planes, void* stream) {
   using namespace lmsf;
   using namespace lmsf::fa;
   if (n_served <= 0) return 0;
@@ -609,7 +609,7 @@ LMSF_API int lmsf_attention_decode_width(const void* q, long long q_stride, void
   a.counters = (unsigned*)scratch;
   a.part_o = scratch ? reinterpret_cast<float*>((unsigned char*)scratch + kDecodeCounterBytes) : nullptr;
   a.part_lse = a.part_o ? a.part_o + (size_t)n_seqs_total * n_q_heads * n_splits * HD : nullptr;
-  if (!make_paged_kv(a.kv, cache, page_stride, block_size, n_kv_heads))
+  if (!make_paged_kv(a.kv, cache, page_stride, block_size, n_kv_heads, HD, kv_planes))
     LMSF_REFUSE("attention: block_size=%d must be a power of two", block_size);
   a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = seq_ids; a.cu_q = cu_q; a.ctx_len = ctx_len;
   a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = n_splits;
@@ -691,7 +691,8 @@ LMSF_API int lmsf_attention_decode_items(const void* q, long long q_stride, void
                                          const void* cache, long long page_stride, int block_size, int n_kv_heads,
                                          const int* block_table, int max_blocks, const void* items, int capacity,
                                          int n_seqs_total, const int* cu_q, const int* ctx_len, float scale, int window,
-                                         int n_q_heads, int head_dim, int block_warps, void* scratch, void* stream) {
+                                         int n_q_heads, int head_dim, int block_warps, void* scratch, int kv_planes,
+                                         void* stream) {
   using namespace lmsf;
   using namespace lmsf::fa;
   if (capacity <= 0) return 0;
@@ -712,7 +713,7 @@ LMSF_API int lmsf_attention_decode_items(const void* q, long long q_stride, void
   a.counters = (unsigned*)scratch;
   a.part_o = reinterpret_cast<float*>((unsigned char*)scratch + kDecodeCounterBytes);
   a.part_lse = a.part_o + (size_t)capacity * n_q_heads * HD;
-  if (!make_paged_kv(a.kv, cache, page_stride, block_size, n_kv_heads))
+  if (!make_paged_kv(a.kv, cache, page_stride, block_size, n_kv_heads, HD, kv_planes))
     LMSF_REFUSE("attention: block_size=%d must be a power of two", block_size);
   a.block_table = block_table; a.max_blocks = max_blocks; a.seq_ids = nullptr; a.cu_q = cu_q; a.ctx_len = ctx_len;
   a.scale = scale; a.window = window; a.n_q_heads = n_q_heads; a.group = group; a.n_splits = 1;
@@ -731,7 +732,7 @@ LMSF_API int lmsf_attention_decode(const void* q, long long q_stride, void* out,
                                    int n_q_heads, int head_dim, int n_splits, void* scratch, void* stream) {
   return lmsf_attention_decode_width(q, q_stride, out, out_stride, cache, page_stride, block_size, n_kv_heads, block_table,
                                      max_blocks, seq_ids, n_served, n_seqs_total, cu_q, ctx_len, scale, window, n_q_heads,
-                                     head_dim, n_splits, 0, scratch, stream);
+                                     head_dim, n_splits, 0, scratch, 2, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

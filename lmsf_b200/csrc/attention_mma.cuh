@@ -43,17 +43,20 @@ constexpr int kThreads = 128;   // 4 warps
 
 // Geometry of one layer's cache and of one request's block table.  block_size is a power of two.
 struct PagedKV {
-  const bf16* cache;        // [page][2][kv_head][slot][HD]
+  const bf16* cache;        // [page][planes][kv_head][slot][HD]
   long long page_stride;    // elements between pages
   int block_size, block_shift;
   int n_kv_heads;
+  long long v_off;          // elements from a key's row to its value's row; 0 when one cached vector is both (planes = 1)
 };
 
-__host__ inline bool make_paged_kv(PagedKV& kv, const void* cache, long long page_stride, int block_size, int n_kv_heads) {
-  if (block_size <= 0 || (block_size & (block_size - 1))) return false;
+__host__ inline bool make_paged_kv(PagedKV& kv, const void* cache, long long page_stride, int block_size, int n_kv_heads,
+                                   int head_dim, int planes = 2) {
+  if (block_size <= 0 || (block_size & (block_size - 1)) || (planes != 1 && planes != 2)) return false;
   int sh = 0;
   while ((1 << sh) < block_size) ++sh;
-  kv = PagedKV{(const bf16*)cache, page_stride, block_size, sh, n_kv_heads};
+  kv = PagedKV{(const bf16*)cache, page_stride, block_size, sh, n_kv_heads,
+               planes == 2 ? (long long)n_kv_heads * block_size * head_dim : 0};
   return true;
 }
 
@@ -82,7 +85,7 @@ template <int HD, int TILE = kTileKeys, int THREADS = kThreads>
 __device__ __forceinline__ void load_stage(uint32_t stage_base, const PagedKV& kv, const int* __restrict__ table, int kvh,
                                            int key0, int lo, int hi, int table_off = 0) {
   using S = Stage<HD, TILE>;
-  const size_t v_off = (size_t)kv.n_kv_heads * kv.block_size * HD;
+  const size_t v_off = (size_t)kv.v_off;
   const size_t head_off = (size_t)kvh * kv.block_size * HD;
   const int mask = kv.block_size - 1;
   if constexpr (THREADS % S::kChunks == 0) {

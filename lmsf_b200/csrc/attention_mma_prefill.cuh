@@ -177,7 +177,7 @@ LMSF_API int lmsf_attention_prefill(const void* q, long long q_stride, void* out
                                     const void* cache, long long page_stride, int block_size, int n_kv_heads,
                                     const int* block_table, int max_blocks, const int* tile_seq, const int* tile_q0,
                                     int n_tiles, const int* cu_q, const int* ctx_len, float scale, int window,
-                                    int n_q_heads, int head_dim, void* stream) {
+                                    int n_q_heads, int head_dim, int kv_planes, void* stream) {
   using namespace lmsf;
   using namespace lmsf::fa;
   if (n_tiles <= 0) return 0;
@@ -188,7 +188,7 @@ LMSF_API int lmsf_attention_prefill(const void* q, long long q_stride, void* out
   if (block_size <= 0 || max_blocks <= 0) LMSF_REFUSE("attention_prefill: bad block table geometry");
   PrefillArgs a;
   a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
-  if (!make_paged_kv(a.kv, cache, page_stride, block_size, n_kv_heads))
+  if (!make_paged_kv(a.kv, cache, page_stride, block_size, n_kv_heads, HD, kv_planes))
     LMSF_REFUSE("attention: block_size=%d must be a power of two", block_size);
   a.block_table = block_table; a.max_blocks = max_blocks; a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
   a.cu_q = cu_q; a.ctx_len = ctx_len; a.scale = scale; a.window = window; a.n_q_heads = n_q_heads;

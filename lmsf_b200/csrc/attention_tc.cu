@@ -134,7 +134,7 @@ __device__ __forceinline__ void gather_tile(uint32_t dst_tile, const PagedKV& kv
                                             int kvh, bool is_v, int key0, int lo, int hi, int lane) {
   constexpr int kChunks = HD / 8;
   constexpr int kRowsPerPass = 32 / kChunks;
-  const size_t head_off = ((size_t)(is_v ? kv.n_kv_heads : 0) + kvh) * kv.block_size * HD;
+  const size_t head_off = (is_v ? (size_t)kv.v_off : 0) + (size_t)kvh * kv.block_size * HD;
   const int mask = kv.block_size - 1;
   const int c = lane % kChunks, r0 = lane / kChunks;
   const uint32_t col = (c / 8) * (BN * 128);
@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
         // range without a page (beyond the sequence, or before the window) is read from page 0 instead: all its
         // keys are masked, and the softmax warps clear those rows of v.
         const int n_box = BN / a.rows_box;
-        const int head_row = (is_v ? a.kv.n_kv_heads : 0) + u.kvh;
+        const int head_row = ((is_v && a.kv.v_off != 0) ? a.kv.n_kv_heads : 0) + u.kvh;   // one plane: the key's row is the value's
         auto fetch_page = [&](int t) {
           const int blk = ((u.tile_begin + t) * BN + lane * a.rows_box) >> a.kv.block_shift;
           return (t < u.n_tiles && lane < n_box && blk < a.max_blocks) ? table[blk] : -1;
@@ -705,18 +705,19 @@ __global__ void __launch_bounds__(kThreadsTotal, 1) prefill_tc_kernel(const Args
 // A box is 64 elements x rows_box slots; the engine writes it 128-byte swizzled.  cuTensorMapEncodeTiled is
 // looked up in the driver at run time, so this library does not link against it.
 // The map of a cache, made once per (address, geometry).  Returns nullptr and sets *why on failure.
-inline const CUtensorMap* cache_tensor_map(const void* cache, long long page_stride, int block_size, int n_kv_heads,
+// n_head_rows: kv heads times planes (keys then values, or one plane that is both).
+inline const CUtensorMap* cache_tensor_map(const void* cache, long long page_stride, int block_size, int n_head_rows,
                                            long long n_pages, int rows_box, const char** why) {
   using Key = std::tuple<const void*, long long, int, int, long long>;
   static std::map<Key, CUtensorMap> maps;
   static std::mutex mu;
   std::lock_guard<std::mutex> lock(mu);
-  const Key key{cache, page_stride, block_size, n_kv_heads, n_pages};
+  const Key key{cache, page_stride, block_size, n_head_rows, n_pages};
   auto it = maps.find(key);
   if (it != maps.end()) return &it->second;
   EncodeTiledFn encode = encode_tiled_fn();
   if (!encode) { *why = "the driver has no cuTensorMapEncodeTiled"; return nullptr; }
-  const cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)block_size, (cuuint64_t)(2 * n_kv_heads), (cuuint64_t)n_pages};
+  const cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)block_size, (cuuint64_t)n_head_rows, (cuuint64_t)n_pages};
   const cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)block_size * HD * 2, (cuuint64_t)page_stride * 2};
   const cuuint32_t box[4] = {64, (cuuint32_t)rows_box, 1, 1};
   const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
@@ -741,7 +742,7 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long l
                                        const void* cache, long long page_stride, long long n_pages, int block_size,
                                        int n_kv_heads, const int* block_table, int max_blocks, const int* tile_seq, const int* tile_q0,
                                        int n_tiles, const int* cu_q, const int* ctx_len, float scale, int window,
-                                       int n_q_heads, int head_dim, int* error_flag, void* stream) {
+                                       int n_q_heads, int head_dim, int* error_flag, int kv_planes, void* stream) {
   using namespace lmsf;
   using namespace lmsf::tc;
   if (n_tiles <= 0) return 0;
@@ -756,7 +757,7 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long l
     LMSF_REFUSE("attention_prefill_tc: q, out and the cache must be 16-byte aligned with row strides that are multiples of 8");
   Args a;
   a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
-  if (!make_paged_kv(a.kv, cache, page_stride, block_size, n_kv_heads))
+  if (!make_paged_kv(a.kv, cache, page_stride, block_size, n_kv_heads, HD, kv_planes))
     LMSF_REFUSE("attention_prefill_tc: block_size=%d must be a power of two", block_size);
   a.block_table = block_table; a.max_blocks = max_blocks; a.tile_seq = tile_seq; a.tile_q0 = tile_q0;
   a.cu_q = cu_q; a.ctx_len = ctx_len; a.scale = scale; a.window = window; a.n_q_heads = n_q_heads;
@@ -769,7 +770,7 @@ LMSF_API int lmsf_attention_prefill_tc(const void* q, long long q_stride, long l
   memset(&kv_map, 0, sizeof(kv_map));
   if (a.use_tma) {
     const char* why = "";
-    const CUtensorMap* m = cache_tensor_map(cache, page_stride, block_size, n_kv_heads, n_pages, a.rows_box, &why);
+    const CUtensorMap* m = cache_tensor_map(cache, page_stride, block_size, kv_planes * n_kv_heads, n_pages, a.rows_box, &why);
     if (!m) LMSF_REFUSE("attention_prefill_tc: %s", why);
     kv_map = *m;
   }

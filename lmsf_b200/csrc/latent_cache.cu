@@ -37,7 +37,31 @@ __global__ void __launch_bounds__(128) latent_norm_cache_write_kernel(const T* _
     dst[i] = i < rank ? from_f32<T>((to_f32(xr[i]) * inv) * w[i]) : from_f32<T>(0.f);
 }
 
+// x[t, h, :] *= sigmoid(gate[t, h]): a gate per token and head on the attention's output.
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, long long x_stride, const T* __restrict__ gate, long long gate_stride,
+                                 int heads, int head_dim) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < heads * head_dim; i += blockDim.x) {
+    const float g = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * gate_stride + i / head_dim])));
+    T* p = x + (size_t)t * x_stride + i;
+    *p = from_f32<T>(to_f32(*p) * g);
+  }
+}
+
 }  // namespace lmsf
+
+LMSF_API int lmsf_head_gate(void* x, long long x_stride, const void* gate, long long gate_stride, int n, int heads,
+                            int head_dim, int dtype, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (heads <= 0 || head_dim <= 0) LMSF_REFUSE("head_gate: heads=%d head_dim=%d", heads, head_dim);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == LMSF_F32) head_gate_kernel<float><<<n, 256, 0, s>>>((float*)x, x_stride, (const float*)gate, gate_stride, heads, head_dim);
+  else if (dtype == LMSF_BF16) head_gate_kernel<bf16><<<n, 256, 0, s>>>((bf16*)x, x_stride, (const bf16*)gate, gate_stride, heads, head_dim);
+  else LMSF_REFUSE("head_gate: unknown dtype code %d", dtype);
+  return LMSF_LAUNCH_STATUS();
+}
 
 // x: rows of [n, rank] of `dtype` (row stride x_stride); w: float32 [rank]; cache: [pages, 1, 1, block_size, padded].
 LMSF_API int lmsf_latent_norm_cache_write(const void* x, long long x_stride, const float* w, void* cache,

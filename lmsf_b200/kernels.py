@@ -478,12 +478,13 @@ def _mma_defines(head_dim: int) -> Tuple[str, ...]:
     return (f"LMSF_HEAD_DIM={head_dim}", f"LMSF_KV_STAGES={MMA_KV_STAGES}")
 
 
-def _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, what):
+def _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, what, kv_planes=2):
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError(f"{what}: bfloat16 only")
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_q_heads * head_dim or out.shape != q.shape:
         raise KernelError(f"{what}: q and out must be [n, heads * head_dim] with a contiguous last dimension")
-    if not cache.is_contiguous() or tuple(cache.shape[1:]) != (2, n_kv_heads, block_size, head_dim):
+    if kv_planes not in (1, 2) or not cache.is_contiguous() or \
+            tuple(cache.shape[1:]) != (kv_planes, n_kv_heads, block_size, head_dim):
         raise KernelError(f"{what}: cache of shape {tuple(cache.shape)} does not match the heads")
     if (q.data_ptr() | out.data_ptr()) % 4 or (q.stride(0) | out.stride(0)) % 2 or cache.data_ptr() % 16:
         raise KernelError(f"{what}: q/out rows must be 4-byte aligned and the cache 16-byte aligned")
@@ -582,13 +583,14 @@ def attention_decode_scratch_floats(n_seqs_total: int, n_q_heads: int, n_splits:
 def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                      block_size: int, seq_ids: Optional[torch.Tensor], n_served: int, cu_q: torch.Tensor,
                      ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int,
-                     head_dim: int, n_splits: int, scratch: Optional[torch.Tensor], warps: int = 0):
+                     head_dim: int, n_splits: int, scratch: Optional[torch.Tensor], warps: int = 0, kv_planes: int = 2):
     """Attention of requests that bring ONE query token each (row cu_q[s] of q), over their ctx_len[s] keys
     in pages.  seq_ids: int32 [n_served] rows of the block table that are served (None: all, in order).
     scratch: float32, at least attention_decode_scratch_floats(...) values when n_splits > 1, all zero when it is
     first used (torch.zeros); the kernel leaves its counters zero, so one buffer serves every later call.
-    warps: the width of the blocks, 4 or 2 (decode_plan chooses it with n_splits); 0 leaves it to the kernel."""
-    _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_decode")
+    warps: the width of the blocks, 4 or 2 (decode_plan chooses it with n_splits); 0 leaves it to the kernel.
+    kv_planes 1: the cache holds one vector per token and kv head that is key and value at once."""
+    _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_decode", kv_planes)
     n_total = block_table.shape[0]
     need = attention_decode_scratch_floats(n_total, n_q_heads, n_splits, head_dim)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
@@ -599,11 +601,11 @@ def attention_decode(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, bl
     f = _func("attention_mma.cu", "lmsf_attention_decode_width",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
                c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p,
-               c_void_p], d)
+               c_int, c_void_p], d)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
            _i32(block_table, "block_table"), block_table.shape[1], _i32(seq_ids, "seq_ids"), n_served, n_total,
            _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale), int(window or 0), n_q_heads, head_dim,
-           n_splits, warps, _ptr(scratch) if need else None, _stream())
+           n_splits, warps, _ptr(scratch) if need else None, int(kv_planes), _stream())
     _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
 
 
@@ -636,38 +638,39 @@ def decode_build_items(items: torch.Tensor, ctx_len: torch.Tensor, seq_ids: Opti
 def attention_decode_items(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                            block_size: int, items: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor,
                            scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int, warps: int,
-                           scratch: torch.Tensor):
+                           scratch: torch.Tensor, kv_planes: int = 2):
     """attention_decode with splits per request, over a list made by decode_build_items.  scratch: float32, at
     least attention_decode_items_scratch_floats(capacity, ...) values, zero when first used."""
-    _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_decode_items")
+    _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_decode_items", kv_planes)
     need = attention_decode_items_scratch_floats(items.shape[0], n_q_heads, head_dim)
     if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
         raise KernelError(f"attention_decode_items: a list of {items.shape[0]} entries needs {need} float32 values of scratch")
     d = _mma_defines(head_dim)
     f = _func("attention_mma.cu", "lmsf_attention_decode_items",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
-               c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p], d)
+               c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p], d)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
            _i32(block_table, "block_table"), block_table.shape[1], _ptr(items), items.shape[0], block_table.shape[0],
            _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale), int(window or 0), n_q_heads, head_dim, int(warps),
-           _ptr(scratch), _stream())
+           _ptr(scratch), int(kv_planes), _stream())
     _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
 
 
 def attention_prefill(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       block_size: int, tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
-                      ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int):
+                      ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                      kv_planes: int = 2):
     """Attention of prompt portions.  Tile i covers the query tokens tile_q0[i] .. tile_q0[i] + 63 (counted
     inside the portion) of request tile_seq[i]."""
-    _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_prefill")
+    _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_prefill", kv_planes)
     d = _mma_defines(head_dim)
     f = _func("attention_mma.cu", "lmsf_attention_prefill",
               [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
-               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p], d)
+               c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p], d)
     rc = f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), block_size, n_kv_heads,
            _i32(block_table, "block_table"), block_table.shape[1], _i32(tile_seq, "tile_seq"),
            _i32(tile_q0, "tile_q0"), n_tiles, _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale),
-           int(window or 0), n_q_heads, head_dim, _stream())
+           int(window or 0), n_q_heads, head_dim, int(kv_planes), _stream())
     _check(rc, "attention_mma.cu", "lmsf_attention_mma", d)
 
 
@@ -684,19 +687,19 @@ def tc_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
 def attention_prefill_tc(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                          block_size: int, tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
                          ctx_len: torch.Tensor, scale: float, window: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
-                         error_flag: Optional[torch.Tensor] = None):
+                         error_flag: Optional[torch.Tensor] = None, kv_planes: int = 2):
     """Attention of prompt portions on tcgen05 tensor cores (head size 64 or 128).  Tile i covers the query
     tokens tile_q0[i] .. tile_q0[i] + 127 (counted inside the portion) of request tile_seq[i]."""
-    _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_prefill_tc")
+    _check_paged(q, out, cache, n_q_heads, n_kv_heads, head_dim, block_size, "attention_prefill_tc", kv_planes)
     d = _mma_defines(head_dim)[:1]
     f = _func("attention_tc.cu", "lmsf_attention_prefill_tc",
               [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_longlong, c_int, c_int,
                c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p,
-               c_void_p], d)
+               c_int, c_void_p], d)
     rc = f(_ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(cache), cache.stride(0), cache.shape[0], block_size,
            n_kv_heads, _i32(block_table, "block_table"), block_table.shape[1], _i32(tile_seq, "tile_seq"),
            _i32(tile_q0, "tile_q0"), n_tiles, _i32(cu_q, "cu_q"), _i32(ctx_len, "ctx_len"), float(scale),
-           int(window or 0), n_q_heads, head_dim, _i32(error_flag, "error_flag"), _stream())
+           int(window or 0), n_q_heads, head_dim, _i32(error_flag, "error_flag"), int(kv_planes), _stream())
     _check(rc, "attention_tc.cu", "lmsf_attention_tc", d)
 
 
@@ -815,6 +818,16 @@ def latent_norm_cache_write(x: torch.Tensor, w: torch.Tensor, eps: float, cache:
     rc = f(_ptr(x), x.stride(0), _f32vec(w, rank, "w"), _ptr(cache), cache.stride(0), _i32(positions, "positions"),
            _i32(token_seq, "token_seq"), _i32(block_table, "block_table"), block_table.shape[1], block_size, n, rank, padded,
            float(eps), dtype_code(x.dtype), _i32(error_flag, "error_flag"), _stream())
+    _check(rc, "latent_cache.cu", "lmsf_latent_cache")
+
+
+def head_gate_(x: torch.Tensor, gate: torch.Tensor, heads: int, head_dim: int):
+    """x[t, h, :] *= sigmoid(gate[t, h]) in place.  x: [n, heads * head_dim], gate: [n, heads] (views, last dimension contiguous)."""
+    n = x.shape[0]
+    if x.shape != (n, heads * head_dim) or gate.shape != (n, heads) or x.stride(1) != 1 or gate.stride(1) != 1 or x.dtype != gate.dtype:
+        raise KernelError("head_gate: x [n, heads * head_dim] and gate [n, heads] of one dtype")
+    f = _func("latent_cache.cu", "lmsf_head_gate", [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p])
+    rc = f(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), n, heads, head_dim, dtype_code(x.dtype), _stream())
     _check(rc, "latent_cache.cu", "lmsf_latent_cache")
 
 

@@ -134,77 +134,87 @@ class PagedAttention(Mixer):
         return matmul_tn(out, self.o, bias=self.o_bias)
 
     def attend(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group) -> None:
-        """bfloat16 with a head size up to 128: single tokens go to the split-key decode kernel, longer portions
-        to a tiled prefill kernel (tcgen05 with accumulators in tensor memory for head sizes 64 and 128,
-        mma.sync otherwise).  Everything else, float32 included, runs on the
-        generic kernel, which is also their plain twin."""
-        slopes = self._slopes()
-        if kernels.mma_attention_supported(q.dtype, self.head_dim) and not self.softcap and slopes is None and \
-                not ctx.extras.get("force_generic_attention"):
-            if ctx.n_decode_seqs:
-                max_ctx = ctx.extras.get("decode_max_ctx")
-                if max_ctx is None:
-                    max_ctx = ctx.extras["decode_max_ctx"] = max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1)
-                visible = min(max_ctx, self.window) if self.window else max_ctx
-                # the mean matters to the plan only where it is far below the longest context (a graph names its class)
-                mean_ctx = ctx.extras.get("decode_mean_ctx")
-                if mean_ctx is None:
-                    lens = [c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1]
-                    mean_ctx = ctx.extras["decode_mean_ctx"] = sum(lens) / len(lens)
-                mean_visible = min(mean_ctx, visible)
-                group_size = self.num_heads // self.num_kv_heads
-                all_decode = ctx.n_decode_seqs == ctx.n_seqs
-                if SPLITS_PER_REQUEST and ctx.n_decode_seqs >= 2 and mean_visible * 4 <= visible:
-                    # Requests that differ much in length (a mean of a quarter of the longest and less): splits per
-                    # request, from a list of work items that a kernel makes from the step's context lengths (once a
-                    # step, for all layers of this geometry).  Measured, 8 layers of the 8B shape: one request at
-                    # 30,000 tokens beside 63 at 500: 1.64 ms a step against 2.11 ms with one number of splits for all;
-                    # one at 2,300 beside 63 at 1,200: 1.54 against 1.50 (the list's launch starts after the kernel
-                    # before it and adds up through global memory), hence the threshold.
-                    widths = kernels.decode_widths(self.head_dim, group_size)
-                    pairs = ctx.n_decode_seqs * self.num_kv_heads * ((group_size + 15) // 16)
-                    warps, slots = widths[0][0], widths[0][2][0]
-                    if len(widths) > 1 and pairs > slots:
-                        warps, slots = widths[1][0], widths[1][2][0]
-                    key = ("decode_items", self.num_kv_heads, group_size, slots, self.window or 0)
-                    items = ctx.extras.get(key)
-                    if items is None:
-                        capacity = kernels.decode_items_capacity(ctx.n_decode_seqs, self.num_kv_heads, group_size, slots)
-                        items = ctx.extras[key] = torch.empty((capacity, 4), dtype=torch.int32, device=q.device)
-                        kernels.decode_build_items(items, ctx.ctx_len, None if all_decode else ctx.decode_seq_ids,
-                                                   ctx.n_decode_seqs, self.window or 0, self.num_heads, self.num_kv_heads,
-                                                   self.head_dim, slots)
-                    need = kernels.attention_decode_items_scratch_floats(items.shape[0], self.num_heads, self.head_dim)
-                    scratch = ctx.extras.get("decode_items_scratch")
-                    if scratch is None or scratch.numel() < need:
-                        scratch = ctx.extras["decode_items_scratch"] = torch.zeros(need, dtype=torch.float32, device=q.device)
-                    kernels.attention_decode_items(out, q, kv, group.block_table, group.block_size, items, ctx.cu_q,
-                                                   ctx.ctx_len, self.scale, self.window or 0, self.num_heads,
-                                                   self.num_kv_heads, self.head_dim, warps, scratch)
-                    splits = None
-                else:
-                    splits, warps = kernels.decode_plan(ctx.n_decode_seqs, self.num_kv_heads, group_size, visible,
-                                                        self.head_dim, kernels.decode_widths(self.head_dim, group_size),
-                                                        mean_ctx=mean_visible if mean_visible * 4 <= visible * 3 else None)
-                if splits is not None:
-                    need = kernels.attention_decode_scratch_floats(ctx.n_seqs, self.num_heads, splits, self.head_dim)
-                    scratch = ctx.extras.get("decode_scratch")
-                    if need and (scratch is None or scratch.numel() < need):
-                        scratch = ctx.extras["decode_scratch"] = torch.zeros(need, dtype=torch.float32, device=q.device)
-                    kernels.attention_decode(out, q, kv, group.block_table, group.block_size,
-                                             None if all_decode else ctx.decode_seq_ids, ctx.n_decode_seqs, ctx.cu_q,
-                                             ctx.ctx_len, self.scale, self.window or 0, self.num_heads,
-                                             self.num_kv_heads, self.head_dim, splits, scratch if need else None, warps)
-            if ctx.n_q_tiles and USE_TC_PREFILL and kernels.tc_attention_supported(q.dtype, self.head_dim):
-                kernels.attention_prefill_tc(out, q, kv, group.block_table, group.block_size, ctx.q_tile128_seq,
-                                             ctx.q_tile128_q0, ctx.n_q_tiles128, ctx.cu_q, ctx.ctx_len, self.scale,
-                                             self.window or 0, self.num_heads, self.num_kv_heads, self.head_dim,
-                                             ctx.error_flag)
-            elif ctx.n_q_tiles:
-                kernels.attention_prefill(out, q, kv, group.block_table, group.block_size, ctx.q_tile_seq,
-                                          ctx.q_tile_q0, ctx.n_q_tiles, ctx.cu_q, ctx.ctx_len, self.scale,
-                                          self.window or 0, self.num_heads, self.num_kv_heads, self.head_dim)
-            return
-        kernels.attention_generic(out, q, kv, group.block_table, group.block_size, ctx.token_seq, ctx.positions,
-                                  self.scale, self.window or 0, self.num_heads, self.num_kv_heads, self.head_dim,
-                                  softcap=self.softcap, slopes=slopes)
+        paged_attend(ctx, out, q, kv, group, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+                     scale=self.scale, window=self.window, softcap=self.softcap, slopes=self._slopes())
+
+
+def paged_attend(ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group, *, num_heads: int,
+                 num_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None, softcap: float = 0.0,
+                 slopes: Optional[torch.Tensor] = None, kv_planes: int = 2) -> None:
+    """Attention over pages for any mix of tokens.  bfloat16 with a head size up to 128: single tokens go to the
+    split-key decode kernel, longer portions to a tiled prefill kernel (tcgen05 with accumulators in tensor memory for
+    head sizes 64 and 128, mma.sync otherwise).  Everything else, float32 included, runs on the generic kernel, which is
+    also their plain twin.  kv_planes 1: one cached vector per token and kv head is key and value at once (the fast
+    kernels only; the caller keeps its own plain kernel for that layout)."""
+    if kernels.mma_attention_supported(q.dtype, head_dim) and not softcap and slopes is None and \
+            not ctx.extras.get("force_generic_attention"):
+        if ctx.n_decode_seqs:
+            max_ctx = ctx.extras.get("decode_max_ctx")
+            if max_ctx is None:
+                max_ctx = ctx.extras["decode_max_ctx"] = max(c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1)
+            visible = min(max_ctx, window) if window else max_ctx
+            # the mean matters to the plan only where it is far below the longest context (a graph names its class)
+            mean_ctx = ctx.extras.get("decode_mean_ctx")
+            if mean_ctx is None:
+                lens = [c for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1]
+                mean_ctx = ctx.extras["decode_mean_ctx"] = sum(lens) / len(lens)
+            mean_visible = min(mean_ctx, visible)
+            group_size = num_heads // num_kv_heads
+            all_decode = ctx.n_decode_seqs == ctx.n_seqs
+            if SPLITS_PER_REQUEST and ctx.n_decode_seqs >= 2 and mean_visible * 4 <= visible:
+                # Requests that differ much in length (a mean of a quarter of the longest and less): splits per
+                # request, from a list of work items that a kernel makes from the step's context lengths (once a
+                # step, for all layers of this geometry).  Measured, 8 layers of the 8B shape: one request at
+                # 30,000 tokens beside 63 at 500: 1.64 ms a step against 2.11 ms with one number of splits for all;
+                # one at 2,300 beside 63 at 1,200: 1.54 against 1.50 (the list's launch starts after the kernel
+                # before it and adds up through global memory), hence the threshold.
+                widths = kernels.decode_widths(head_dim, group_size)
+                pairs = ctx.n_decode_seqs * num_kv_heads * ((group_size + 15) // 16)
+                warps, slots = widths[0][0], widths[0][2][0]
+                if len(widths) > 1 and pairs > slots:
+                    warps, slots = widths[1][0], widths[1][2][0]
+                key = ("decode_items", num_kv_heads, group_size, slots, window or 0)
+                items = ctx.extras.get(key)
+                if items is None:
+                    capacity = kernels.decode_items_capacity(ctx.n_decode_seqs, num_kv_heads, group_size, slots)
+                    items = ctx.extras[key] = torch.empty((capacity, 4), dtype=torch.int32, device=q.device)
+                    kernels.decode_build_items(items, ctx.ctx_len, None if all_decode else ctx.decode_seq_ids,
+                                               ctx.n_decode_seqs, window or 0, num_heads, num_kv_heads,
+                                               head_dim, slots)
+                need = kernels.attention_decode_items_scratch_floats(items.shape[0], num_heads, head_dim)
+                scratch = ctx.extras.get("decode_items_scratch")
+                if scratch is None or scratch.numel() < need:
+                    scratch = ctx.extras["decode_items_scratch"] = torch.zeros(need, dtype=torch.float32, device=q.device)
+                kernels.attention_decode_items(out, q, kv, group.block_table, group.block_size, items, ctx.cu_q,
+                                               ctx.ctx_len, scale, window or 0, num_heads,
+                                               num_kv_heads, head_dim, warps, scratch, kv_planes=kv_planes)
+                splits = None
+            else:
+                splits, warps = kernels.decode_plan(ctx.n_decode_seqs, num_kv_heads, group_size, visible,
+                                                    head_dim, kernels.decode_widths(head_dim, group_size),
+                                                    mean_ctx=mean_visible if mean_visible * 4 <= visible * 3 else None)
+            if splits is not None:
+                need = kernels.attention_decode_scratch_floats(ctx.n_seqs, num_heads, splits, head_dim)
+                scratch = ctx.extras.get("decode_scratch")
+                if need and (scratch is None or scratch.numel() < need):
+                    scratch = ctx.extras["decode_scratch"] = torch.zeros(need, dtype=torch.float32, device=q.device)
+                kernels.attention_decode(out, q, kv, group.block_table, group.block_size,
+                                         None if all_decode else ctx.decode_seq_ids, ctx.n_decode_seqs, ctx.cu_q,
+                                         ctx.ctx_len, scale, window or 0, num_heads,
+                                         num_kv_heads, head_dim, splits, scratch if need else None, warps,
+                                         kv_planes=kv_planes)
+        if ctx.n_q_tiles and USE_TC_PREFILL and kernels.tc_attention_supported(q.dtype, head_dim):
+            kernels.attention_prefill_tc(out, q, kv, group.block_table, group.block_size, ctx.q_tile128_seq,
+                                         ctx.q_tile128_q0, ctx.n_q_tiles128, ctx.cu_q, ctx.ctx_len, scale,
+                                         window or 0, num_heads, num_kv_heads, head_dim,
+                                         ctx.error_flag, kv_planes=kv_planes)
+        elif ctx.n_q_tiles:
+            kernels.attention_prefill(out, q, kv, group.block_table, group.block_size, ctx.q_tile_seq,
+                                      ctx.q_tile_q0, ctx.n_q_tiles, ctx.cu_q, ctx.ctx_len, scale,
+                                      window or 0, num_heads, num_kv_heads, head_dim, kv_planes=kv_planes)
+        return
+    if kv_planes != 2:
+        raise ValueError("the plain attention kernel of keys and values takes a cache of two planes")
+    kernels.attention_generic(out, q, kv, group.block_table, group.block_size, ctx.token_seq, ctx.positions,
+                              scale, window or 0, num_heads, num_kv_heads, head_dim,
+                              softcap=softcap, slopes=slopes)

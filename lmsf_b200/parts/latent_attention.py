@@ -19,7 +19,10 @@ import torch
 
 from .. import kernels
 from .base import KVCacheSpec, LayerCache, Mixer, StepContext, WeightSpec, register_part
+from .attention import paged_attend
 from .linear import batched_matmul_tn, matmul_tn
+
+USE_FAST_KERNELS = True     # bfloat16: the tensor-core attention kernels on the one-plane cache
 
 
 @register_part("mixer", "latent_attention")
@@ -88,5 +91,15 @@ class LatentAttention(Mixer):
         return matmul_tn(out, self.o)
 
     def attend(self, ctx: StepContext, out: torch.Tensor, q: torch.Tensor, kv: torch.Tensor, group, gate) -> None:
+        """bfloat16 with a padded rank up to 128: the engine's tensor-core attention kernels (split-key decode, tcgen05
+        or mma.sync prefill) with one kv head of `padded_rank` values whose cached vector is key and value at once;
+        the gate is a small kernel after them.  float32 and larger ranks: the plain kernel, gate included."""
+        if USE_FAST_KERNELS and kernels.mma_attention_supported(q.dtype, self.padded_rank) and \
+                not ctx.extras.get("force_generic_attention"):
+            paged_attend(ctx, out, q, kv, group, num_heads=self.num_heads, num_kv_heads=1, head_dim=self.padded_rank,
+                         scale=self.scale, window=self.window, kv_planes=1)
+            if gate is not None:
+                kernels.head_gate_(out, gate, self.num_heads, self.padded_rank)
+            return
         kernels.attention_shared_kv(out, q, kv, group.block_table, group.block_size, ctx.token_seq, ctx.positions,
                                     self.scale, self.window or 0, self.num_heads, self.padded_rank, gate=gate)

@@ -468,3 +468,63 @@ def test_greedy_generation_through_the_engine():
             if got != nxt:                             # only a near tie may be decided otherwise
                 assert float(top2[0] - lg[got]) <= 1e-4 * float(lg.abs().max())
             toks.append(got)
+
+
+# ----------------------------------------------------------------------------- the tensor-core attention kernels on a cache of one plane
+
+def _hand_made_context(seqs, block_size, n_pages, rng, window):
+    """A StepContext for requests [(cached tokens, new tokens)] with randomly chosen pages; pages that the window has
+    passed before the step are given back (-1), as the cache manager does."""
+    from lmsf_b200.parts.base import CacheGroupView, StepContext
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    pos, tseq, cu, ctx_lens, q_lens = [], [], [0], [], []
+    max_blocks = max((s + n + block_size - 1) // block_size for s, n in seqs)
+    table = torch.full((len(seqs), max_blocks), -1, dtype=torch.int32)
+    free = list(range(n_pages))
+    rng.shuffle(free)
+    for i, (start, n) in enumerate(seqs):
+        pos += list(range(start, start + n))
+        tseq += [i] * n
+        cu.append(cu[-1] + n)
+        ctx_lens.append(start + n)
+        q_lens.append(n)
+        first_seen = max(0, start - window + 1) if window else 0
+        for b in range((start + n + block_size - 1) // block_size):
+            if (b + 1) * block_size > first_seen:
+                table[i, b] = free.pop()
+    dec = [i for i, (_, n) in enumerate(seqs) if n == 1]
+    tiles = lambda size: [(i, q0) for i, (_, n) in enumerate(seqs) if n > 1 for q0 in range(0, n, size)]
+    t64, t128 = tiles(64), tiles(128)
+    return StepContext(n_tokens=len(pos), n_seqs=len(seqs), dtype=torch.bfloat16, device=torch.device(DEV), token_ids=i32([0] * len(pos)),
+                       positions=i32(pos), token_seq=i32(tseq), cu_q=i32(cu), ctx_len=i32(ctx_lens), state_slot=i32([0] * len(seqs)),
+                       groups=[CacheGroupView(table.to(DEV), block_size)], q_lens=q_lens, ctx_lens=ctx_lens, state_slots=[0] * len(seqs),
+                       error_flag=torch.zeros(1, dtype=torch.int32, device=DEV), decode_seq_ids=i32(dec or [0]), n_decode_seqs=len(dec),
+                       q_tile_seq=i32([t[0] for t in t64] or [0]), q_tile_q0=i32([t[1] for t in t64] or [0]), n_q_tiles=len(t64),
+                       q_tile128_seq=i32([t[0] for t in t128] or [0]), q_tile128_q0=i32([t[1] for t in t128] or [0]), n_q_tiles128=len(t128))
+
+
+@pytest.mark.parametrize("rank,heads,window,block_size", [(64, 4, 72, 16), (24, 3, 9, 8), (128, 5, 40, 16), (48, 2, None, 16), (64, 17, 130, 32)])
+def test_tensor_core_attention_on_one_cached_vector_agrees_with_the_plain_kernel(rank, heads, window, block_size):
+    """Prompt portions (from the start, from the middle of a window, across several query tiles) and single tokens (just
+    past a window, at a page's first and last slot, at position 0) in one batch: the split-key decode kernel and the tiled
+    prefill kernels read the cache's one plane as key and as value; the plain kernel is their twin."""
+    from lmsf_b200 import kernels
+    from lmsf_b200.parts.latent_attention import LatentAttention
+    rng = random.Random(rank + heads)
+    g = torch.Generator().manual_seed(rank * 7 + heads)
+    part = LatentAttention(hidden_size=32, num_heads=heads, head_dim=16, value_dim=16, kv_rank=rank, eps=1e-5, scale=0.3, window=window)
+    Rp = part.padded_rank
+    w = window or 0
+    seqs = [(0, 150), (37, 90), (w + 3, 1), (2 * block_size - 1, 1), (2 * block_size, 1), (0, 1), (200, 2), (max(w - 1, 1), 1), (500, 1)]
+    for batch in (seqs, [s for s in seqs if s[1] == 1], [s for s in seqs if s[1] > 1]):
+        ctx = _hand_made_context(batch, block_size, 200, rng, window)
+        cache = (torch.randn(201, 1, 1, block_size, Rp, generator=g) * 0.7).bfloat16().to(DEV)
+        cache[..., rank:] = 0
+        q = torch.randn(ctx.n_tokens, heads * Rp, generator=g).bfloat16().to(DEV)
+        gate = torch.randn(ctx.n_tokens, heads, generator=g).bfloat16().to(DEV)
+        fast, plain = torch.zeros_like(q), torch.zeros_like(q)
+        part.attend(ctx, fast, q, cache, ctx.groups[0], gate)
+        kernels.attention_shared_kv(plain, q, cache, ctx.groups[0].block_table, block_size, ctx.token_seq, ctx.positions, 0.3, w, heads, Rp, gate=gate)
+        assert int(ctx.error_flag.item()) == 0
+        diff = (fast.float() - plain.float()).abs().max(dim=1).values.cpu()
+        assert float(diff.max()) <= 2e-2 * float(plain.float().abs().max()), (len(batch), int(diff.argmax()), float(diff.max()))
