@@ -16,7 +16,34 @@ namespace lmsf {
 constexpr int kThreads = 256;
 constexpr int kMaxPerThread = 64;   // widths up to 16,384
 
-template <typename T, int PER>
+// V consecutive values of a row as floats (V = 4: one 16-byte or 8-byte access; V = 1: any width and alignment)
+template <int V> __device__ __forceinline__ void ld_vec(const float* p, float (&v)[V]) {
+  if (V == 4) { const float4 x = *reinterpret_cast<const float4*>(p); v[0] = x.x; v[1 % V] = x.y; v[2 % V] = x.z; v[3 % V] = x.w; }
+  else v[0] = *p;
+}
+template <int V> __device__ __forceinline__ void ld_vec(const bf16* p, float (&v)[V]) {
+  if (V == 4) {
+    const uint2 x = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.y));
+    v[0] = a.x; v[1 % V] = a.y; v[2 % V] = b.x; v[3 % V] = b.y;
+  } else v[0] = __bfloat162float(*p);
+}
+template <int V> __device__ __forceinline__ void st_vec(float* p, const float (&v)[V]) {
+  if (V == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1 % V], v[2 % V], v[3 % V]);
+  else *p = v[0];
+}
+template <int V> __device__ __forceinline__ void st_vec(bf16* p, const float (&v)[V]) {
+  if (V == 4) {
+    uint2 x;
+    *reinterpret_cast<__nv_bfloat162*>(&x.x) = __floats2bfloat162_rn(v[0], v[1 % V]);
+    *reinterpret_cast<__nv_bfloat162*>(&x.y) = __floats2bfloat162_rn(v[2 % V], v[3 % V]);
+    *reinterpret_cast<uint2*>(p) = x;
+  } else *p = __float2bfloat16_rn(v[0]);
+}
+
+// PER passes of kThreads threads with V values each cover a row.
+template <typename T, int PER, int V>
 __global__ void __launch_bounds__(kThreads) stream_norm_kernel(float* __restrict__ res, const T* __restrict__ y,
                                                                const float* __restrict__ w_post, const float* __restrict__ ls,
                                                                const float* __restrict__ first, const float* __restrict__ vec,
@@ -24,47 +51,72 @@ __global__ void __launch_bounds__(kThreads) stream_norm_kernel(float* __restrict
                                                                int hidden, float eps_post, float eps_next) {
   __shared__ float scratch[33];
   const size_t base = (size_t)blockIdx.x * hidden;
-  float v[PER];
-  float r[PER];
+  float v[PER][V];
+  float r[PER][V];
   pdl_launch_dependents();
   pdl_wait();
   float ss = 0.f;
   if (y != nullptr) {
 #pragma unroll
     for (int it = 0; it < PER; ++it) {
-      const int i = it * kThreads + threadIdx.x;
-      v[it] = i < hidden ? to_f32(y[base + i]) : 0.f;
-      ss = fmaf(v[it], v[it], ss);
+      const int i = (it * kThreads + threadIdx.x) * V;
+      if (i < hidden) ld_vec<V>(y + base + i, v[it]);
+#pragma unroll
+      for (int e = 0; e < V; ++e) { if (i >= hidden) v[it][e] = 0.f; ss = fmaf(v[it][e], v[it][e], ss); }
     }
     ss = block_sum(ss, scratch);
   }
   const float inv_post = 1.0f / sqrtf(ss / (float)hidden + eps_post);
+  const bool changes = y != nullptr || first != nullptr || vec != nullptr;
   float s2 = 0.f;
 #pragma unroll
   for (int it = 0; it < PER; ++it) {
-    const int i = it * kThreads + threadIdx.x;
-    float x = 0.f;
+    const int i = (it * kThreads + threadIdx.x) * V;
+#pragma unroll
+    for (int e = 0; e < V; ++e) r[it][e] = 0.f;
     if (i < hidden) {
-      x = res[base + i];
+      ld_vec<V>(res + base + i, r[it]);
       if (y != nullptr) {
-        float b = (v[it] * inv_post) * w_post[i];
-        if (ls != nullptr) b *= ls[i];
-        x += b;
+        float wp[V], l[V];
+        ld_vec<V>(w_post + i, wp);
+        if (ls != nullptr) ld_vec<V>(ls + i, l);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          float b = (v[it][e] * inv_post) * wp[e];
+          if (ls != nullptr) b *= l[e];
+          r[it][e] += b;
+        }
       }
-      if (first != nullptr) x += first[base + i];
-      if (vec != nullptr) x += vec[i];
-      if (y != nullptr || first != nullptr || vec != nullptr) res[base + i] = x;
+      if (first != nullptr) {
+        float f[V];
+        ld_vec<V>(first + base + i, f);
+#pragma unroll
+        for (int e = 0; e < V; ++e) r[it][e] += f[e];
+      }
+      if (vec != nullptr) {
+        float f[V];
+        ld_vec<V>(vec + i, f);
+#pragma unroll
+        for (int e = 0; e < V; ++e) r[it][e] += f[e];
+      }
+      if (changes) st_vec<V>(res + base + i, r[it]);
     }
-    r[it] = x;
-    s2 = fmaf(x, x, s2);
+#pragma unroll
+    for (int e = 0; e < V; ++e) s2 = fmaf(r[it][e], r[it][e], s2);
   }
   if (h == nullptr) return;
   s2 = block_sum(s2, scratch);
   const float inv = 1.0f / sqrtf(s2 / (float)hidden + eps_next);
 #pragma unroll
   for (int it = 0; it < PER; ++it) {
-    const int i = it * kThreads + threadIdx.x;
-    if (i < hidden) h[base + i] = from_f32<T>((r[it] * inv) * w_next[i]);
+    const int i = (it * kThreads + threadIdx.x) * V;
+    if (i < hidden) {
+      float wn[V], o[V];
+      ld_vec<V>(w_next + i, wn);
+#pragma unroll
+      for (int e = 0; e < V; ++e) o[e] = (r[it][e] * inv) * wn[e];
+      st_vec<V>(h + base + i, o);
+    }
   }
 }
 
@@ -102,20 +154,27 @@ __global__ void __launch_bounds__(kThreads) embed_norm_kernel(float* __restrict_
   }
 }
 
-template <typename T, int PER>
+template <typename T, int PER, int V>
 static int launch_stream(float* res, const void* y, const float* w_post, const float* ls, const float* first,
                          const float* vec, void* h, const float* w_next, int n, int hidden, float eps_post, float eps_next,
                          cudaStream_t s) {
-  return launch_pdl(stream_norm_kernel<T, PER>, dim3(n), dim3(kThreads), 0, s, res, (const T*)y, w_post, ls, first, vec,
+  return launch_pdl(stream_norm_kernel<T, PER, V>, dim3(n), dim3(kThreads), 0, s, res, (const T*)y, w_post, ls, first, vec,
                     (T*)h, w_next, hidden, eps_post, eps_next);
 }
 
 template <typename T>
-static int pick_stream(int per, float* res, const void* y, const float* w_post, const float* ls, const float* first,
+static int pick_stream(float* res, const void* y, const float* w_post, const float* ls, const float* first,
                        const float* vec, void* h, const float* w_next, int n, int hidden, float eps_post, float eps_next,
                        cudaStream_t s) {
-#define LMSF_CASE(P) if (per <= P) return launch_stream<T, P>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s)
-  LMSF_CASE(1); LMSF_CASE(2); LMSF_CASE(4); LMSF_CASE(8); LMSF_CASE(16); LMSF_CASE(32); LMSF_CASE(64);
+  // four values per thread and access where the rows allow it (every pointer is then 8- or 16-byte aligned)
+  const bool wide = hidden % 4 == 0 && ((uintptr_t)res | (uintptr_t)first | (uintptr_t)w_post | (uintptr_t)ls | (uintptr_t)vec |
+                                        (uintptr_t)w_next) % 16 == 0 && ((uintptr_t)y | (uintptr_t)h) % (4 * sizeof(T)) == 0;
+  const int per = ceil_div(hidden, kThreads * (wide ? 4 : 1));
+#define LMSF_CASE(P)                                                                                                          \
+  if (per <= P) return wide ? launch_stream<T, P, 4>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s) \
+                            : launch_stream<T, P, 1>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s)
+  LMSF_CASE(1); LMSF_CASE(2); LMSF_CASE(4); LMSF_CASE(8); LMSF_CASE(16);
+  if (!wide) { LMSF_CASE(32); LMSF_CASE(64); }
 #undef LMSF_CASE
   return LMSF_EBADARG;
 }
@@ -133,11 +192,10 @@ LMSF_API int lmsf_stream_norm(float* res, const void* y, const float* w_post, co
   if (y != nullptr && w_post == nullptr) LMSF_REFUSE("stream_norm: a branch needs the weight of its norm");
   if (h != nullptr && w_next == nullptr) LMSF_REFUSE("stream_norm: an output needs the weight of its norm");
   if ((y != nullptr && !(eps_post > 0.f)) || (h != nullptr && !(eps_next > 0.f))) LMSF_REFUSE("stream_norm: eps must be positive");
-  const int per = ceil_div(hidden, kThreads);
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
-  if (dtype == LMSF_F32) rc = pick_stream<float>(per, res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s);
-  else if (dtype == LMSF_BF16) rc = pick_stream<bf16>(per, res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s);
+  if (dtype == LMSF_F32) rc = pick_stream<float>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s);
+  else if (dtype == LMSF_BF16) rc = pick_stream<bf16>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s);
   else LMSF_REFUSE("stream_norm: unknown dtype code %d", dtype);
   return rc;
 }

@@ -763,10 +763,14 @@ LIGHTNING_MAX_DK = 256
 
 def lightning_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor,
                    decay: torch.Tensor, cu_q: torch.Tensor, state_slot: torch.Tensor, n_seqs: int, heads: int, dk: int,
-                   dv: int, act: Optional[str] = "silu"):
+                   dv: int, act: Optional[str] = "silu", items: Optional[torch.Tensor] = None,
+                   scratch: Optional[torch.Tensor] = None, mode: int = 0):
     """Per request (tokens cu_q[s]..cu_q[s+1]) and head: S = decay S + act(k_t) act(v_t)^T, out_t = S^T act(q_t), with
     S = state[state_slot[s], head] (float32 [dk, dv]) read before and written after.  q, k: [n, heads * dk] and
-    v: [n, heads * dv] views with a contiguous last dimension; out: float32 [n, heads * dv]."""
+    v: [n, heads * dv] views with a contiguous last dimension; out: float32 [n, heads * dv].
+    items (int32 [n_items, 4]: request, first token, end token, index in scratch): the launch serves these instead of
+    every request whole.  mode 1: every item from a zero state, its final state to scratch[index] (no outputs);
+    mode 2: every item from the state in scratch[index], outputs only (see lightning_prefix)."""
     n = q.shape[0]
     for name, t, width in (("q", q, heads * dk), ("k", k, heads * dk), ("v", v, heads * dv)):
         if t.dim() != 2 or t.shape != (n, width) or t.stride(1) != 1 or t.dtype != q.dtype:
@@ -777,12 +781,35 @@ def lightning_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch
         raise KernelError(f"lightning: the state must be contiguous float32 [slots, {heads}, {dk}, {dv}]")
     if decay.dtype != torch.float32 or decay.shape != (heads,) or not decay.is_contiguous():
         raise KernelError("lightning: one float32 decay per head")
+    n_items = n_seqs
+    if items is not None:
+        if items.dtype != torch.int32 or items.dim() != 2 or items.shape[1] != 4 or not items.is_contiguous():
+            raise KernelError("lightning: items must be a contiguous int32 tensor [n_items, 4]")
+        n_items = items.shape[0]
+    if mode != 0 and (items is None or scratch is None or scratch.dtype != torch.float32 or not scratch.is_contiguous()
+                      or tuple(scratch.shape[1:]) != (heads, dk, dv)):
+        raise KernelError(f"lightning: modes 1 and 2 need items and a float32 scratch [chunks, {heads}, {dk}, {dv}]")
     f = _func("lightning.cu", "lmsf_lightning_scan",
               [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
-               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
     rc = f(_ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(out), out.stride(0), _ptr(state),
-           _ptr(decay), _i32(cu_q, "cu_q"), _i32(state_slot, "state_slot"), n_seqs, heads, dk, dv, LIGHTNING_ACTS[act],
-           dtype_code(q.dtype), _stream())
+           _ptr(decay), _i32(cu_q, "cu_q"), _i32(state_slot, "state_slot"), n_items, heads, dk, dv, LIGHTNING_ACTS[act],
+           dtype_code(q.dtype), _ptr(items), _ptr(scratch), int(mode), _stream())
+    _check(rc, "lightning.cu", "lmsf_lightning")
+
+
+def lightning_prefix(scratch: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, state_slot: torch.Tensor,
+                     items: torch.Tensor, spans: torch.Tensor):
+    """Between the two passes over chunks: scratch[c] (what chunk c adds from a zero state) becomes the state before chunk
+    c, in the order of each request's chunks; the state after the last chunk goes to the request's slot.
+    spans: int32 [n, 4] = (request, first chunk item, end chunk item, 0)."""
+    heads, dk, dv = state.shape[1:]
+    if spans.dtype != torch.int32 or spans.dim() != 2 or spans.shape[1] != 4 or not spans.is_contiguous():
+        raise KernelError("lightning: spans must be a contiguous int32 tensor [n, 4]")
+    f = _func("lightning.cu", "lmsf_lightning_prefix",
+              [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    rc = f(_ptr(scratch), _ptr(state), _ptr(decay), _i32(state_slot, "state_slot"), _ptr(items), _ptr(spans), spans.shape[0],
+           heads, dk, dv, _stream())
     _check(rc, "lightning.cu", "lmsf_lightning")
 
 

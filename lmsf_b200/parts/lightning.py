@@ -7,8 +7,8 @@
 
 q, k, v and the gate come from one merged product; the activation is applied by the scan kernel as it reads them
 (float32, from the stored value); the state, the decays and o are float32; norm and gate are one kernel.
-Prompt portions and single tokens run on the same kernel (csrc/lightning.cu), so the state after a prompt is the same
-bits however the prompt was cut.
+Prompt portions and single tokens run on the same kernel (csrc/lightning.cu); portions of LONG_PORTION tokens and more
+are cut into chunks that run in parallel (two passes of that kernel around a prefix over the chunks' states).
 """
 from __future__ import annotations
 
@@ -19,6 +19,10 @@ import torch
 from .. import kernels
 from .base import LayerCache, Mixer, StateSpec, StepContext, WeightSpec, register_part
 from .linear import matmul_tn
+
+
+LONG_PORTION = 256      # tokens from which a request's portion is cut into chunks that run in parallel
+CHUNK_TOKENS = 64
 
 
 @register_part("mixer", "lightning_attention")
@@ -59,13 +63,48 @@ class LightningAttention(Mixer):
         self._decay = torch.tensor(self.decay_values, dtype=torch.float32, device=device)
         self._norm32 = self.norm.float().contiguous()
 
+    @staticmethod
+    def _plan(ctx: StepContext):
+        """None when no request brings a long portion.  Else (short, chunks, spans), made once a step from the host's copy
+        of the portions' lengths and shared by all layers: `short` lists the requests that run whole (None if there are
+        none), `chunks` cuts every long portion into pieces of CHUNK_TOKENS, `spans` names each long portion's pieces."""
+        if not ctx.q_lens or max(ctx.q_lens) < LONG_PORTION:
+            return None
+        plan = ctx.extras.get("lightning_plan")
+        if plan is None:
+            short, chunks, spans, t0 = [], [], [], 0
+            for s, n in enumerate(ctx.q_lens):
+                if n >= LONG_PORTION:
+                    first = len(chunks)
+                    for c in range(t0, t0 + n, CHUNK_TOKENS):
+                        chunks.append((s, c, min(c + CHUNK_TOKENS, t0 + n), len(chunks)))
+                    spans.append((s, first, len(chunks), 0))
+                else:
+                    short.append((s, t0, t0 + n, 0))
+                t0 += n
+            flat = torch.tensor(short + chunks + spans, dtype=torch.int32).to(ctx.device, non_blocking=True)
+            a, b = len(short), len(short) + len(chunks)
+            plan = ctx.extras["lightning_plan"] = (flat[:a] if a else None, flat[a:b], flat[b:])
+        return plan
+
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         p = matmul_tn(h, self.qkvg)
         a, b = self.qk_size, self.v_size
         q, k, v, g = p[:, :a], p[:, a:2 * a], p[:, 2 * a:2 * a + b], p[:, 2 * a + b:]
         o = torch.empty((ctx.n_tokens, b), dtype=torch.float32, device=p.device)
-        kernels.lightning_scan(o, q, k, v, cache.state, self._decay, ctx.cu_q, ctx.state_slot, ctx.n_seqs, self.num_heads,
-                               self.head_dim, self.value_dim, self.activation)
+        plan = self._plan(ctx)
+        args = (o, q, k, v, cache.state, self._decay, ctx.cu_q, ctx.state_slot, ctx.n_seqs, self.num_heads, self.head_dim,
+                self.value_dim, self.activation)
+        if plan is None:                     # single tokens and short portions: one block row per request
+            kernels.lightning_scan(*args)
+        else:
+            short, chunks, spans = plan
+            if short is not None:
+                kernels.lightning_scan(*args, items=short)
+            scratch = torch.empty((chunks.shape[0], self.num_heads, self.head_dim, self.value_dim), dtype=torch.float32, device=p.device)
+            kernels.lightning_scan(*args, items=chunks, scratch=scratch, mode=1)
+            kernels.lightning_prefix(scratch, cache.state, self._decay, ctx.state_slot, chunks, spans)
+            kernels.lightning_scan(*args, items=chunks, scratch=scratch, mode=2)
         y = torch.empty((ctx.n_tokens, b), dtype=p.dtype, device=p.device)
         kernels.gated_norm(y, o, g, self._norm32, self.eps)
         return matmul_tn(y, self.o)

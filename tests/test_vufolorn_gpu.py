@@ -241,6 +241,51 @@ def test_lightning_scan_in_portions_and_token_by_token(dtype, heads, dk, dv):
         assert torch.equal(part, whole) and torch.equal(st2, st), cuts      # the same operations in the same order
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_lightning_scan_of_a_long_portion_in_parallel_chunks(dtype):
+    """A long portion that starts from a state that is not zero, cut into chunks of unequal size that run in parallel (from
+    a zero state, then a prefix over the chunks' states, then again from the true state), beside a short request that runs
+    whole: outputs and final states agree with the plain recurrence."""
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(17)
+    tdt = TDT[dtype]
+    heads, dk, dv = 3, 40, 48
+    lens = [5, 333]
+    n = sum(lens)
+    q, k, v = (torch.randn(n, heads * d, generator=g).to(tdt) for d in (dk, dk, dv))
+    decay = torch.tensor([0.5, 0.97, 1.0], dtype=torch.float32)
+    S0 = torch.randn(2, heads, dk, dv, generator=g)
+    silu = lambda z: P.silu(z.double())
+    want, states, off = [], [], 0
+    for i, L in enumerate(lens):
+        S = S0[i].double().clone()
+        want.append(plain_scan(silu(q[off:off + L]).view(L, heads, dk), silu(k[off:off + L]).view(L, heads, dk),
+                               silu(v[off:off + L]).view(L, heads, dv), decay.double(), S).reshape(L, heads * dv))
+        states.append(S)
+        off += L
+    want = torch.cat(want)
+    state = torch.zeros(4, heads, dk, dv, device=DEV)
+    state[3], state[1] = dev(S0[0]), dev(S0[1])
+    slots = dev(torch.tensor([3, 1], dtype=torch.int32))
+    cu = dev(torch.tensor([0, 5, n], dtype=torch.int32))
+    cuts = [5, 69, 70, 134, 198, 262, 326, n]                    # the long portion's chunks: 64 tokens, one of 1, a last one of 12
+    chunks = dev(torch.tensor([(1, a, b, i) for i, (a, b) in enumerate(zip(cuts[:-1], cuts[1:]))], dtype=torch.int32))
+    spans = dev(torch.tensor([(1, 0, len(cuts) - 1, 0)], dtype=torch.int32))
+    short = dev(torch.tensor([(0, 0, 5, 0)], dtype=torch.int32))
+    out = torch.zeros(n, heads * dv, device=DEV)
+    scratch = torch.full((len(cuts) - 1, heads, dk, dv), 3.0, device=DEV)
+    args = (out, dev(q), dev(k), dev(v), state, dev(decay), cu, slots, 2, heads, dk, dv, "silu")
+    kernels.lightning_scan(*args, items=short)
+    kernels.lightning_scan(*args, items=chunks, scratch=scratch, mode=1)
+    kernels.lightning_prefix(scratch, state, dev(decay), slots, chunks, spans)
+    kernels.lightning_scan(*args, items=chunks, scratch=scratch, mode=2)
+    tol = 2e-5 if dtype == "float32" else 1e-4
+    assert float((out.cpu().double() - want).abs().max()) <= tol * float(want.abs().max())
+    for i, s in enumerate([3, 1]):
+        assert float((state[s].cpu().double() - states[i]).abs().max()) <= tol * float(states[i].abs().max())
+    assert torch.all(state[0] == 0) and torch.all(state[2] == 0)
+
+
 def test_gated_norm_norms_all_heads_of_a_token_together():
     from lmsf_b200 import kernels
     g = torch.Generator().manual_seed(3)
@@ -370,7 +415,7 @@ def test_every_way_of_cutting_agrees_with_the_plain_implementation(name, dtype):
     """Whole prompts, prefill then token by token, portions of several sizes down to two tokens, and batches of unequal
     requests with few pages and three state slots (pages and slots are used again)."""
     folder, _ = folder_of(name)
-    reqs = requests_for(name, [61, 5, 1, 130, 33, 18, 77])
+    reqs = requests_for(name, [61, 5, 1, 130, 33, 18, 300 if name == "X" else 77])     # 300: a portion long enough for parallel chunks
     ref = oracle(name, reqs)
     bs = BLOCK[name]
     modes = {"whole": traces.whole(reqs), "decode": traces.whole(reqs, tail=30), "portions": traces.portions(reqs, [2, 7, 3, 16, 2, 29]),
