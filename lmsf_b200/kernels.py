@@ -934,9 +934,9 @@ def moe_grouped_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gather: 
     if not moe_grouped_tc_supported(a, w) or a.shape[1] != K or out.shape[1] != N or out.stride(1) != 1:
         raise KernelError(f"moe_tc: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} are not taken")
     f = _func("moe_tc.cu", "lmsf_moe_grouped_tc",
-              [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
-               c_int, c_void_p, c_void_p])
-    rc = f(_ptr(out), _ptr(a), _ptr(w), _i32(gather, "gather"), _i32(tiles, "tiles"), _i32(meta, "meta"), tiles.shape[0], N, K,
+              [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong,
+               c_int, c_int, c_void_p, c_void_p])
+    rc = f(_ptr(out), _ptr(a), _ptr(w), _i32(gather, "gather"), _i32(tiles, "tiles"), _i32(meta, "meta"), tiles.shape[0], E, N, K,
            a.stride(0), out.stride(0), MOE_ACTS[act], dtype_code(out.dtype), _i32(error_flag, "error_flag"), _stream())
     _check(rc, "moe_tc.cu", "lmsf_moe_tc")
 
