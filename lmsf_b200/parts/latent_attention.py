@@ -13,6 +13,7 @@ the attention kernel to its output (it commutes with the linear value expansion)
 """
 from __future__ import annotations
 
+import warnings
 from typing import Dict, Optional
 
 import torch
@@ -64,6 +65,9 @@ class LatentAttention(Mixer):
         return self.q_size + self.kv_rank + self.num_heads + 2 * self.num_heads * self.padded_rank + self.v_size
 
     def prepare(self, dtype, device) -> None:
+        if dtype == torch.bfloat16 and not kernels.mma_attention_supported(dtype, self.padded_rank):
+            warnings.warn(f"kv_rank {self.kv_rank} is beyond the tensor-core attention kernels (up to "
+                          f"{kernels.MMA_MAX_HEAD_DIM}); bfloat16 attention runs on the plain kernel", RuntimeWarning, stacklevel=2)
         H, dk, dv, R, Rp = self.num_heads, self.head_dim, self.value_dim, self.kv_rank, self.padded_rank
         # the key expansion as the query sees it: per head [rank (padded with zero rows), dk]
         uk_t = torch.zeros((H, Rp, dk), dtype=self.uk.dtype, device=self.uk.device)
