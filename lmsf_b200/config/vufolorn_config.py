@@ -95,7 +95,7 @@ class VufolornConfig:
                 mixer.decay = [float(a) for a in decay]
             else:
                 mixer.kv_rank = _pos_int(_need(m, "kv_rank", where + ".mixer"), "kv_rank")
-                mixer.scale = float(_need(m, "scale", where + ".mixer"))
+                mixer.scale = float(m["scale"]) if m.get("scale") is not None else None     # None: dim ** -0.5
                 mask = m.get("mask")
                 if mask and mask.get("size") is not None:
                     mixer.window = _pos_int(mask["size"], "mask.size")

@@ -6,7 +6,7 @@
 // vllm/kernels/attention/attention_kernels.cu:82-414.  Differences: one kernel serves prompt
 // portions and decoded tokens alike (every query token reads its keys from pages, its own key
 // included, which the cache write has stored before); the softmax is exact (no 1e-6 in the
-// denominator, expf rather than __expf); any head size that is a multiple of 16 up to 256.
+// denominator, expf rather than __expf); any head size that is a multiple of 16 up to 512.
 //
 // One block of 4 warps per (query token, query head).  Keys are walked in tiles of 32 that are
 // aligned to absolute positions; tile j belongs to warp j % 4; every warp keeps a running
@@ -19,7 +19,7 @@ LMSF_DEFINE_LAST_ERROR(lmsf_attention_generic)
 
 namespace lmsf {
 
-constexpr int kMaxHeadDim = 256;
+constexpr int kMaxHeadDim = 512;
 constexpr int kWarps = 4;
 
 struct GenericAttnArgs {

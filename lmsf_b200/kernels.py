@@ -205,6 +205,9 @@ def rope_cache_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[tor
 
 # ----------------------------------------------------------------------------- attention (generic)
 
+GENERIC_MAX_HEAD_DIM = 512     # the plain attention kernel holds a head's accumulator in registers up to this size
+
+
 def attention_generic(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       block_size: int, token_seq: torch.Tensor, positions: torch.Tensor, scale: float, window: int,
                       n_q_heads: int, n_kv_heads: int, head_dim: int, softcap: float = 0.0,

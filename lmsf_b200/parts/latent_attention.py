@@ -35,8 +35,8 @@ class LatentAttention(Mixer):
         self.hidden_size, self.num_heads, self.head_dim, self.value_dim = int(hidden_size), int(num_heads), int(head_dim), int(value_dim)
         self.kv_rank = int(kv_rank)
         self.padded_rank = (self.kv_rank + 15) // 16 * 16
-        if self.padded_rank > 256:
-            raise ValueError(f"kv_rank {kv_rank} is beyond the attention kernels (up to 256)")
+        if self.padded_rank > kernels.GENERIC_MAX_HEAD_DIM:
+            raise ValueError(f"kv_rank {kv_rank} is beyond the attention kernels (up to {kernels.GENERIC_MAX_HEAD_DIM})")
         self.eps = float(eps)
         self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
         self.window = int(window) if window else None

@@ -226,12 +226,12 @@ def test_attention_refuses_sizes_it_was_not_written_for():
                                   torch.zeros(1, 1, dtype=torch.int32, device=d), 4,
                                   torch.zeros(1, dtype=torch.int32, device=d), torch.zeros(1, dtype=torch.int32, device=d),
                                   1.0, 0, 2, 2, 24)
-    q = torch.zeros(1, 272, device=d)
+    q = torch.zeros(1, 528, device=d)              # beyond the plain kernel's largest head (512)
     with pytest.raises(kernels.KernelError):
-        kernels.attention_generic(torch.empty_like(q), q, torch.zeros(1, 2, 1, 4, 272, device=d),
+        kernels.attention_generic(torch.empty_like(q), q, torch.zeros(1, 2, 1, 4, 528, device=d),
                                   torch.zeros(1, 1, dtype=torch.int32, device=d), 4,
                                   torch.zeros(1, dtype=torch.int32, device=d), torch.zeros(1, dtype=torch.int32, device=d),
-                                  1.0, 0, 1, 1, 272)
+                                  1.0, 0, 1, 1, 528)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -309,8 +309,9 @@ def _paged_latents(c, block_size, n_pages, padded, dtype, rng):
     return cache, pages
 
 
+@pytest.mark.parametrize("R", [32, 272])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_attention_over_one_cached_vector_sees_exactly_its_window(dtype):
+def test_attention_over_one_cached_vector_sees_exactly_its_window(dtype, R):
     """One key is made to stand out (a large c aligned with the query); the output must be that key's c when it is the
     oldest key inside the window, and must not contain it when it is one further back; the same at a page border, for a
     key far back without a window, and for the first tokens of a sequence."""
@@ -318,7 +319,7 @@ def test_attention_over_one_cached_vector_sees_exactly_its_window(dtype):
     tdt = TDT[dtype]
     rng = random.Random(5)
     g = torch.Generator().manual_seed(5)
-    heads, R, bs = 3, 32, 8
+    heads, bs = 3, 8
     T = 300
     for window, qpos, hot in [(9, 100, 92), (9, 100, 91), (16, 47, 32), (16, 47, 31), (8, 15, 8), (8, 15, 7),
                               (0, 299, 3), (0, 299, 0), (5, 2, 0), (1, 40, 40), (1, 40, 39), (72, 271, 200), (72, 271, 199)]:
