@@ -932,7 +932,7 @@ def moe_grouped_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 def moe_grouped_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gather: Optional[torch.Tensor], tiles: torch.Tensor,
                    meta: torch.Tensor, act: Optional[str] = None, error_flag: Optional[torch.Tensor] = None):
-    """`moe_grouped` on the tensor cores (bfloat16 operands, tiles of MOE_TC_TILE_ROWS rows; out bfloat16 or float32)."""
+    """`moe_grouped` on the tensor cores (bfloat16 operands, a tile list of MOE_TC_TILE_ROWS rows a tile; out bfloat16 or float32)."""
     E, N, K = w.shape
     if not moe_grouped_tc_supported(a, w) or a.shape[1] != K or out.shape[1] != N or out.stride(1) != 1:
         raise KernelError(f"moe_tc: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} are not taken")
