@@ -574,3 +574,52 @@ def test_tensor_core_attention_on_one_cached_vector_agrees_with_the_plain_kernel
         assert int(ctx.error_flag.item()) == 0
         diff = (fast.float() - plain.float()).abs().max(dim=1).values.cpu()
         assert float(diff.max()) <= 2e-2 * float(plain.float().abs().max()), (len(batch), int(diff.argmax()), float(diff.max()))
+
+
+# ----------------------------------------------------------------------------- random configurations
+
+def random_config(seed):
+    """Sizes that are no multiples of anything in particular: widths that 8 does not divide, odd head counts, ranks and
+    windows around page borders, every optional piece present or absent by chance."""
+    rng = random.Random(seed)
+    width = rng.choice([36, 50, 72, 100, 136])
+    layers = []
+    for _ in range(rng.randint(2, 4)):
+        heads = rng.randint(1, 5)
+        mlp = None
+        if rng.random() < 0.8:
+            experts = rng.randint(1, 9)
+            mlp = moe(experts, rng.randint(1, experts), rng.choice([8, 12, 20, 40]), rng.choice([0, 0, 10, 24]))
+        if rng.random() < 0.5:
+            layer = lightning(heads, rng.choice([4, 10, 16, 36]), rng.choice([6, 16, 33, 70]),
+                              [rng.choice([0.3, 0.8, 0.95, 0.999, 1.0]) for _ in range(heads)])
+        else:
+            layer = latent(heads, rng.choice([4, 12, 16, 40]), rng.choice([6, 16, 24]), rng.choice([8, 20, 32, 48, 130]),
+                           rng.choice([None, 1, 3, 8, 17, 33]), rng.choice([0.1, 0.3, 0.6]))
+        layers.append(with_mlp(layer, mlp))
+    cfg = {"architecture": "Vufolorn", "vocab": rng.choice([61, 128, 257]), "width": width,
+           "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-3])}, "layers": layers}
+    if rng.random() < 0.7:
+        start = rng.randint(0, len(layers) - 1)
+        cfg["loop"] = {"start": start, "stop": rng.randint(start + 1, len(layers)), "times": rng.randint(1, 3)}
+    return cfg
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations(seed):
+    name = f"R{seed}"
+    CONFIGS[name] = random_config(seed)
+    folder, _ = folder_of(name)
+    rng = random.Random(seed)
+    reqs = requests_for(name, [rng.randint(1, 70) for _ in range(4)], seed=seed)
+    ref = oracle(name, reqs)
+    bs = rng.choice([8, 16, 32])
+    for dtype in ("float32", "bfloat16"):
+        for steps in (traces.whole(reqs, tail=5), traces.mixed(reqs, seed=seed, max_live=2, tail=4)):
+            out = traces.run_inprocess(folder, dtype, steps, bs, traces.max_live_tokens(steps, 64), max_live=2)
+            rows = traces.collect(steps, out)
+            if dtype == "float32":
+                assert worst_rel(rows, ref) <= 5e-5, (CONFIGS[name], worst_rel(rows, ref))
+            else:
+                e = position_errors(rows, ref)
+                assert e[len(e) // 2] <= 2e-2, (CONFIGS[name], e[len(e) // 2])
