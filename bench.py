@@ -470,7 +470,7 @@ def main() -> int:
                     help="instead of the contract's line: 64 requests of 128..2048 prompt tokens and 256 generated "
                          "tokens each through the engine's continuous batching")
     ap.add_argument("--design", default=None, choices=["vufolorn"],
-                    help="instead of the contract's line: prefill and decode tokens/s of that design at two layer sizes "
+                    help="instead of the default line: prefill and decode tokens/s of that design at two layer sizes "
                          "beside the Llama shape of equal width, and its kernels alone against their rooflines")
     a = ap.parse_args()
     if a.design is not None:
