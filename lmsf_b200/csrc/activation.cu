@@ -46,6 +46,38 @@ __global__ void gated_act_vec_kernel(bf16* __restrict__ out, const bf16* __restr
   }
 }
 
+// Gate and up clamped before the product: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + 1).
+template <typename T>
+__global__ void clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ in, int d, long long in_stride, float limit, float alpha) {
+  const T* row = in + (size_t)blockIdx.x * in_stride;
+  T* o = out + (size_t)blockIdx.x * d;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < d; i += gridDim.y * blockDim.x) {
+    const float g = fminf(to_f32(row[i]), limit);
+    const float u = fminf(fmaxf(to_f32(row[d + i]), -limit), limit);
+    o[i] = from_f32<T>((g / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+  }
+}
+
+// out[t, i] = gelu_tanh(a[t, i]) * table[ids[t], offset + i]: a gate that a per-token vector from a table passes.
+template <typename T>
+__global__ void gelu_mul_gather_kernel(T* __restrict__ out, const T* __restrict__ a, long long a_stride, const T* __restrict__ table,
+                                       long long table_stride, int offset, const int* __restrict__ ids, int vocab, int d,
+                                       int* __restrict__ error_flag) {
+  const int t = blockIdx.x, id = ids[t];
+  const bool ok = id >= 0 && id < vocab;
+  if (!ok && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
+  const T* e = table + (size_t)(ok ? id : 0) * table_stride + offset;
+  for (int i = threadIdx.x; i < d; i += blockDim.x)
+    out[(size_t)t * d + i] = from_f32<T>(ok ? act_gelu_tanh(to_f32(a[(size_t)t * a_stride + i])) * to_f32(e[i]) : 0.f);
+}
+
+// x <- cap * tanh(x * scale / cap) (cap 0: x * scale), float32 in place: logits scaled and capped smoothly.
+__global__ void scale_softcap_kernel(float* __restrict__ x, long long n, float scale, float cap) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) { const float z = x[i] * scale; x[i] = cap > 0.f ? cap * tanhf(z / cap) : z; }
+}
+
 // x[t, i] += bias[i], the sum taken in float32 and rounded once to x's type.
 template <typename T>
 __global__ void bias_add_kernel(T* __restrict__ x, const T* __restrict__ bias, int d, long long stride) {
@@ -98,5 +130,44 @@ LMSF_API int lmsf_gated_act(void* out, const void* in, int n, int d, long long i
   if (dtype == LMSF_F32) { if (act == kActSilu) LMSF_GA(float, kActSilu); else LMSF_GA(float, kActGeluTanh); }
   else { if (act == kActSilu) LMSF_GA(bf16, kActSilu); else LMSF_GA(bf16, kActGeluTanh); }
 #undef LMSF_GA
+  return LMSF_LAUNCH_STATUS();
+}
+
+// in: [n, 2 * d] (gate first, up second); out: [n, d]; see clamped_glu_kernel.
+LMSF_API int lmsf_clamped_glu(void* out, const void* in, int n, int d, long long in_stride, float limit, float alpha, int dtype,
+                              void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (d <= 0 || in_stride < 2LL * d || !(limit > 0.f)) LMSF_REFUSE("clamped_glu: d=%d, in_stride=%lld, limit=%g", d, in_stride, limit);
+  int gy = ceil_div(d, 256 * 4);
+  if (gy > 64) gy = 64;
+  dim3 grid(n, gy);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == LMSF_F32) clamped_glu_kernel<float><<<grid, 256, 0, s>>>((float*)out, (const float*)in, d, in_stride, limit, alpha);
+  else if (dtype == LMSF_BF16) clamped_glu_kernel<bf16><<<grid, 256, 0, s>>>((bf16*)out, (const bf16*)in, d, in_stride, limit, alpha);
+  else LMSF_REFUSE("clamped_glu: unknown dtype code %d", dtype);
+  return LMSF_LAUNCH_STATUS();
+}
+
+// out: [n, d] contiguous; a: [n, d] with a_stride; table: [vocab, table_stride] of which columns offset .. offset + d are taken.
+LMSF_API int lmsf_gelu_mul_gather(void* out, const void* a, long long a_stride, const void* table, long long table_stride,
+                                  int offset, const int* ids, int vocab, int n, int d, int dtype, int* error_flag, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (d <= 0 || offset < 0 || offset + d > table_stride) LMSF_REFUSE("gelu_mul_gather: columns %d..%d of %lld", offset, offset + d, table_stride);
+  const int threads = d >= 256 ? 256 : (d >= 64 ? 64 : 32);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == LMSF_F32)
+    gelu_mul_gather_kernel<float><<<n, threads, 0, s>>>((float*)out, (const float*)a, a_stride, (const float*)table, table_stride, offset, ids, vocab, d, error_flag);
+  else if (dtype == LMSF_BF16)
+    gelu_mul_gather_kernel<bf16><<<n, threads, 0, s>>>((bf16*)out, (const bf16*)a, a_stride, (const bf16*)table, table_stride, offset, ids, vocab, d, error_flag);
+  else LMSF_REFUSE("gelu_mul_gather: unknown dtype code %d", dtype);
+  return LMSF_LAUNCH_STATUS();
+}
+
+LMSF_API int lmsf_scale_softcap(float* x, long long n, float scale, float cap, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  scale_softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, n, scale, cap);
   return LMSF_LAUNCH_STATUS();
 }

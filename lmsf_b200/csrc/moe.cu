@@ -62,6 +62,78 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, long long ld, 
   }
 }
 
+// Routing by sigmoid scores inside the best groups of neighbouring experts.  s = sigmoid(logit); the choice is made by
+// s + correction; a group's score is the sum of its two largest choice scores (of its one, if it has one expert); only
+// experts of the `keep` best groups can be chosen; the weights are the chosen experts' s (times `weight_scale`), not
+// renormalised.  Ties go to the lower number.  One warp per token; shared memory: per warp experts + n_groups floats.
+__global__ void moe_topk_sigmoid_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ correction,
+                                        int n, int experts, int top, int n_groups, int keep, float weight_scale,
+                                        int* __restrict__ ids, float* __restrict__ wts) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= n) return;
+  float* c = sm + (size_t)warp * (experts + n_groups);
+  float* gs = c + experts;
+  for (int e = lane; e < experts; e += 32) {
+    const float z = logits[(size_t)t * ld + e];
+    c[e] = 1.0f / (1.0f + expf(-z)) + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (n_groups > 1 && keep < n_groups) {
+    const int size = experts / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;             // the largest and the second
+      for (int i = 0; i < size; ++i) {
+        const float v = c[g * size + i];
+        if (v > a) { b = a; a = v; } else if (v > b) b = v;
+      }
+      gs[g] = size > 1 ? a + b : a;
+    }
+    __syncwarp();
+    for (int j = 0; j < keep; ++j) {                   // the kept groups are marked by +infinity
+      float best = -INFINITY;
+      int arg = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32)
+        if (gs[g] != INFINITY && gs[g] > best) { best = gs[g]; arg = g; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
+      }
+      __syncwarp();
+      if (lane == 0 && arg != 0x7fffffff) gs[arg] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (gs[e / size] != INFINITY) c[e] = -INFINITY;
+    __syncwarp();
+  }
+  int mine_id = 0;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32)
+      if (c[e] > best) { best = c[e]; arg = e; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (arg == 0x7fffffff) arg = 0;                   // fewer allowed experts than choices: a configuration fault
+    if (j == lane) mine_id = arg;
+    __syncwarp();
+    if (lane == 0) c[arg] = -INFINITY;
+    __syncwarp();
+  }
+  if (lane < top) {
+    ids[(size_t)t * top + lane] = mine_id;
+    wts[(size_t)t * top + lane] = weight_scale / (1.0f + expf(-logits[(size_t)t * ld + mine_id]));
+  }
+}
+
 // One block.  ids: [pairs]; offsets: [experts + 1]; pair_row: [pairs] row of each pair in expert order;
 // row_token: [pairs] token of each row; tiles: [max_tiles][4] = (expert, first row, rows, 0); meta[0] = number of tiles.
 __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ ids, int pairs, int top, int experts,
@@ -211,6 +283,20 @@ LMSF_API int lmsf_moe_topk(const float* logits, long long ld, const float* bias,
   if (experts <= 0 || experts > kMaxExperts || top <= 0 || top > experts || top > 32)
     LMSF_REFUSE("moe: %d choices of %d experts (up to %d experts, up to 32 choices)", top, experts, kMaxExperts);
   moe_topk_kernel<<<ceil_div(n, 4), 128, 0, (cudaStream_t)stream>>>(logits, ld, bias, n, experts, top, ids, wts);
+  return LMSF_LAUNCH_STATUS();
+}
+
+LMSF_API int lmsf_moe_topk_sigmoid(const float* logits, long long ld, const float* correction, int n, int experts, int top,
+                                   int n_groups, int keep, float weight_scale, int* ids, float* wts, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (experts <= 0 || experts > kMaxExperts || top <= 0 || top > experts || top > 32)
+    LMSF_REFUSE("moe: %d choices of %d experts (up to %d experts, up to 32 choices)", top, experts, kMaxExperts);
+  if (n_groups < 1 || experts % n_groups || keep < 1 || keep > n_groups || (long long)keep * (experts / n_groups) < top)
+    LMSF_REFUSE("moe: %d experts in %d groups of which %d are kept cannot give %d choices", experts, n_groups, keep, top);
+  const size_t smem = (size_t)4 * (experts + n_groups) * sizeof(float);
+  moe_topk_sigmoid_kernel<<<ceil_div(n, 4), 128, smem, (cudaStream_t)stream>>>(logits, ld, correction, n, experts, top, n_groups,
+                                                                             keep, weight_scale, ids, wts);
   return LMSF_LAUNCH_STATUS();
 }
 

@@ -1,0 +1,299 @@
+// Recurrent mixers whose per-request state is one [dk, dv] matrix per head that every token decays, writes and reads
+// (selective state-space layers with a scalar decay per head and token; the gated delta rule), and what stands around
+// them: the short causal convolution over time with its carried inputs, and the norm over groups of columns with a gate.
+//
+//   causal_conv   y[t, c] = act(b[c] + sum_j w[c, j] * x[t - (taps - 1) + j, c]); inputs before a portion's first token
+//                 come from the request's state slot ([taps - 1, channels] float32), which is rolled on afterwards
+//   gated_scan    per request, head and token, in this order:
+//                   dt = softplus(raw_dt + dt_bias[h]);  a = exp(-exp(a_log[h]) * dt)
+//                   plain rule:  S <- a S + (dt k) v^T                      (k_times_dt; the write is k v^T without it)
+//                   delta rule:  S <- a S;  u = sigmoid(raw_beta) (v - S^T k);  S <- S + k u^T
+//                   o = S^T q (+ skip[h] v)
+//                 q and k may be made unit vectors first (x / sqrt(sum x^2 + eps), q times a constant); several heads may
+//                 share one q/k head.  The state, the decays and every sum are float32; the order of the sums does not
+//                 depend on how a request's tokens are cut into steps.
+//   grouped_gated_norm   out = norm_g(x) * w * act(gate)   or   out = norm_g(x * act(gate)) * w, the root mean square
+//                 taken over each group of `gsize` columns, the weight indexed by column modulo its length
+//
+// The state of a head is stored transposed, [dv][dk]: the eight threads that share a column read consecutive rows.
+#include "common.cuh"
+
+LMSF_DEFINE_LAST_ERROR(lmsf_recurrent)
+
+namespace lmsf {
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// ---------------------------------------------------------------------------------------------- convolution
+
+constexpr int kConvChannels = 64;    // channels per block (threadIdx.x)
+constexpr int kConvChunk = 256;      // tokens per block along gridDim.z
+constexpr int kMaxTaps = 8;
+
+// grid (channel tiles, requests, token chunks); block (64, lanes): lanes of tokens side by side.
+// Only the block of a request's first chunk reads its state, and only that block writes it (after its outputs):
+// later chunks start at least kConvChunk >= taps - 1 tokens into the portion.
+template <typename T>
+__global__ void causal_conv_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ x, long long x_stride,
+                                   const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ state,
+                                   long long slot_stride, const int* __restrict__ cu_q, const int* __restrict__ state_slot,
+                                   int C, int taps, int act) {
+  const int c = blockIdx.x * kConvChannels + threadIdx.x;
+  const int s = blockIdx.y;
+  const int t0 = cu_q[s], n = cu_q[s + 1] - t0;
+  const int lo = blockIdx.z * kConvChunk;
+  if (lo >= n) return;
+  const int hi = min(n, lo + kConvChunk);
+  float* st = state + (size_t)state_slot[s] * slot_stride;      // [taps - 1][C]
+  if (c < C) {
+    float wr[kMaxTaps];
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j) wr[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+    const float b = bias ? bias[c] : 0.f;
+    for (int t = lo + threadIdx.y; t < hi; t += blockDim.y) {
+      float acc = b;
+#pragma unroll
+      for (int j = 0; j < kMaxTaps; ++j) {
+        if (j < taps) {
+          const int u = t - (taps - 1) + j;                     // place in the portion; negative: before it
+          const float v = u >= 0 ? to_f32(x[(size_t)(t0 + u) * x_stride + c]) : st[(size_t)(taps - 1 + u) * C + c];
+          acc = fmaf(wr[j], v, acc);
+        }
+      }
+      out[(size_t)(t0 + t) * out_stride + c] = from_f32<T>(act ? silu_f(acc) : acc);
+    }
+  }
+  if (blockIdx.z != 0) return;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < C) {
+    // the last taps - 1 inputs, oldest first; row i reads row i + n of the old state (n >= 1: never a row already written)
+    for (int i = 0; i < taps - 1; ++i) {
+      const int u = n - (taps - 1) + i;
+      const float v = u >= 0 ? to_f32(x[(size_t)(t0 + u) * x_stride + c]) : st[(size_t)(taps - 1 + u) * C + c];
+      st[(size_t)i * C + c] = v;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- scan
+
+struct ScanArgs {
+  float* out; long long out_stride;                            // [n, H * dv]
+  const void* q; const void* k; const void* v;                 // q, k: [n, G * dk]; v: [n, H * dv]
+  long long q_stride, k_stride, v_stride;
+  const void* dt; long long dt_stride;                         // [n, H] raw step sizes
+  const void* beta; long long beta_stride;                     // [n, H] raw write strengths (delta rule) or null
+  const float* dt_bias; const float* a_log; const float* skip; // [H]; skip may be null
+  float* state; long long slot_stride;                         // per slot [H][dv][dk] at the start
+  const int* cu_q; const int* state_slot;
+  int H, G, dk, dv;
+  int k_times_dt, unit_qk;
+  float unit_eps, q_scale;
+};
+
+constexpr int kScanTokens = 16;     // tokens staged in shared memory at a time
+constexpr int kScanCols = 32;       // columns of the state per block
+
+// grid (column tiles, heads, requests); 256 threads: thread = (column c = tid / 8, row lane r = tid % 8), rows r + 8 m.
+template <typename T, int ROWS, bool DELTA>
+__global__ void __launch_bounds__(256) gated_scan_kernel(ScanArgs a) {
+  constexpr int DKP = 8 * ROWS;
+  __shared__ float sq[kScanTokens][DKP];
+  __shared__ float sk[kScanTokens][DKP];
+  __shared__ float sv[kScanTokens][kScanCols];
+  __shared__ float sa[kScanTokens], sb[kScanTokens];
+  const int tid = threadIdx.x, c = tid >> 3, r = tid & 7, lane = tid & 31, warp = tid >> 5;
+  const int head = blockIdx.y, seq = blockIdx.z, col = blockIdx.x * kScanCols + c;
+  const int g = head / (a.H / a.G);
+  const int t0 = a.cu_q[seq], n = a.cu_q[seq + 1] - t0;
+  if (n <= 0) return;
+  float* st = a.state + (size_t)a.state_slot[seq] * a.slot_stride + (size_t)head * a.dv * a.dk;
+  const bool live = col < a.dv;
+  float S[ROWS];
+#pragma unroll
+  for (int m = 0; m < ROWS; ++m) {
+    const int i = r + 8 * m;
+    S[m] = (live && i < a.dk) ? st[(size_t)col * a.dk + i] : 0.f;
+  }
+  const float bias = a.dt_bias[head], rate = expf(a.a_log[head]);
+  const float skip = a.skip ? a.skip[head] : 0.f;
+  for (int base = 0; base < n; base += kScanTokens) {
+    const int cnt = min(kScanTokens, n - base);
+    __syncthreads();
+    for (int tt = warp; tt < cnt; tt += 8) {
+      const size_t t = (size_t)(t0 + base + tt);
+      const T* qp = (const T*)a.q + t * a.q_stride + (size_t)g * a.dk;
+      const T* kp = (const T*)a.k + t * a.k_stride + (size_t)g * a.dk;
+      float fq = 1.f, fk = 1.f;
+      if (a.unit_qk) {
+        float ssq = 0.f, ssk = 0.f;
+        for (int i = lane; i < a.dk; i += 32) {
+          const float x = to_f32(qp[i]), y = to_f32(kp[i]);
+          ssq = fmaf(x, x, ssq);
+          ssk = fmaf(y, y, ssk);
+        }
+        ssq = warp_sum(ssq);
+        ssk = warp_sum(ssk);
+        fq = a.q_scale / sqrtf(ssq + a.unit_eps);
+        fk = 1.0f / sqrtf(ssk + a.unit_eps);
+      }
+      const float dt = softplus_f(to_f32(((const T*)a.dt)[t * a.dt_stride + head]) + bias);
+      if (a.k_times_dt) fk *= dt;
+      for (int i = lane; i < DKP; i += 32) {
+        sq[tt][i] = i < a.dk ? to_f32(qp[i]) * fq : 0.f;
+        sk[tt][i] = i < a.dk ? to_f32(kp[i]) * fk : 0.f;
+      }
+      if (lane == 0) {
+        sa[tt] = expf(-rate * dt);
+        sb[tt] = a.beta ? sigmoid_f(to_f32(((const T*)a.beta)[t * a.beta_stride + head])) : 1.f;
+      }
+      const int cc = blockIdx.x * kScanCols + lane;
+      sv[tt][lane] = cc < a.dv ? to_f32(((const T*)a.v)[t * a.v_stride + (size_t)head * a.dv + cc]) : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < cnt; ++tt) {
+      const float dec = sa[tt], vv = sv[tt][c];
+      if (DELTA) {
+        float p = 0.f;
+#pragma unroll
+        for (int m = 0; m < ROWS; ++m) {
+          S[m] *= dec;
+          p = fmaf(S[m], sk[tt][r + 8 * m], p);
+        }
+        p += __shfl_xor_sync(0xffffffffu, p, 4);
+        p += __shfl_xor_sync(0xffffffffu, p, 2);
+        p += __shfl_xor_sync(0xffffffffu, p, 1);
+        const float u = sb[tt] * (vv - p);
+#pragma unroll
+        for (int m = 0; m < ROWS; ++m) S[m] = fmaf(sk[tt][r + 8 * m], u, S[m]);
+      } else {
+#pragma unroll
+        for (int m = 0; m < ROWS; ++m) S[m] = fmaf(sk[tt][r + 8 * m], vv, dec * S[m]);
+      }
+      float o = 0.f;
+#pragma unroll
+      for (int m = 0; m < ROWS; ++m) o = fmaf(S[m], sq[tt][r + 8 * m], o);
+      o += __shfl_xor_sync(0xffffffffu, o, 4);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      if (r == 0 && live) a.out[(size_t)(t0 + base + tt) * a.out_stride + (size_t)head * a.dv + col] = fmaf(skip, vv, o);
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int m = 0; m < ROWS; ++m) {
+      const int i = r + 8 * m;
+      if (i < a.dk) st[(size_t)col * a.dk + i] = S[m];
+    }
+  }
+}
+
+template <typename T, bool DELTA>
+static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t s) {
+  dim3 grid(ceil_div(a.dv, kScanCols), a.H, n_seqs);
+  const int rows = ceil_div(a.dk, 8);
+#define LMSF_CASE(R) if (rows <= R) { gated_scan_kernel<T, R, DELTA><<<grid, 256, 0, s>>>(a); return LMSF_LAUNCH_STATUS(); }
+  LMSF_CASE(2) LMSF_CASE(4) LMSF_CASE(8) LMSF_CASE(16) LMSF_CASE(32)
+#undef LMSF_CASE
+  return LMSF_EBADARG;
+}
+
+// ---------------------------------------------------------------------------------------------- norm over groups
+
+// A team (a warp, or the whole block) serves one (token, group).
+template <typename T, bool BLOCK>
+__global__ void grouped_gated_norm_kernel(T* __restrict__ out, long long out_stride, const float* __restrict__ x,
+                                          long long x_stride, const T* __restrict__ gate, long long gate_stride,
+                                          const float* __restrict__ w, int wlen, int n, int n_groups, int gsize, float eps,
+                                          int gate_silu, int gate_first) {
+  __shared__ float scratch[33];
+  const int team = BLOCK ? blockIdx.x : blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int me = BLOCK ? threadIdx.x : (threadIdx.x & 31), step = BLOCK ? blockDim.x : 32;
+  if (team >= n * n_groups) return;
+  const int t = team / n_groups, grp = team % n_groups;
+  const float* xr = x + (size_t)t * x_stride + (size_t)grp * gsize;
+  const T* gr = gate ? gate + (size_t)t * gate_stride + (size_t)grp * gsize : nullptr;
+  float ss = 0.f;
+  for (int i = me; i < gsize; i += step) {
+    float v = xr[i];
+    if (gate_first && gr) { const float z = to_f32(gr[i]); v *= gate_silu ? silu_f(z) : sigmoid_f(z); }
+    ss = fmaf(v, v, ss);
+  }
+  ss = BLOCK ? block_sum(ss, scratch) : warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)gsize + eps);
+  T* o = out + (size_t)t * out_stride + (size_t)grp * gsize;
+  for (int i = me; i < gsize; i += step) {
+    float v = xr[i];
+    const float z = gr ? to_f32(gr[i]) : 0.f;
+    const float gv = gr ? (gate_silu ? silu_f(z) : sigmoid_f(z)) : 1.f;
+    if (gate_first) v *= gv;
+    v = (v * inv) * w[(grp * gsize + i) % wlen];
+    if (!gate_first) v *= gv;
+    o[i] = from_f32<T>(v);
+  }
+}
+
+}  // namespace lmsf
+
+// x: [n, C] rows of `dtype` with x_stride elements between tokens; out likewise; w: float32 [C, taps]; bias: float32 [C] or
+// null; state: float32, the [taps - 1, C] block of slot s starts at state + s * slot_stride.  act: 0 none, 1 silu.
+// max_q: the longest portion of the launch (the host's copy; sizes the grid only).
+LMSF_API int lmsf_causal_conv(void* out, long long out_stride, const void* x, long long x_stride, const float* w,
+                              const float* bias, float* state, long long slot_stride, const int* cu_q, const int* state_slot,
+                              int n_seqs, int max_q, int C, int taps, int act, int dtype, void* stream) {
+  using namespace lmsf;
+  if (n_seqs <= 0 || max_q <= 0) return 0;
+  if (C <= 0 || taps < 1 || taps > kMaxTaps) LMSF_REFUSE("causal_conv: %d channels, %d taps (1 to %d taps)", C, taps, kMaxTaps);
+  if (n_seqs > 65535) LMSF_REFUSE("causal_conv: more than 65535 requests in one launch");
+  dim3 grid(ceil_div(C, kConvChannels), n_seqs, ceil_div(max_q, kConvChunk));
+  dim3 block(kConvChannels, max_q >= 4 ? 4 : (max_q >= 2 ? 2 : 1));
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == LMSF_F32)
+    causal_conv_kernel<float><<<grid, block, 0, s>>>((float*)out, out_stride, (const float*)x, x_stride, w, bias, state, slot_stride, cu_q, state_slot, C, taps, act);
+  else if (dtype == LMSF_BF16)
+    causal_conv_kernel<bf16><<<grid, block, 0, s>>>((bf16*)out, out_stride, (const bf16*)x, x_stride, w, bias, state, slot_stride, cu_q, state_slot, C, taps, act);
+  else LMSF_REFUSE("causal_conv: unknown dtype code %d", dtype);
+  return LMSF_LAUNCH_STATUS();
+}
+
+LMSF_API int lmsf_gated_scan(float* out, long long out_stride, const void* q, const void* k, const void* v, long long q_stride,
+                             long long k_stride, long long v_stride, const void* dt, long long dt_stride, const void* beta,
+                             long long beta_stride, const float* dt_bias, const float* a_log, const float* skip, float* state,
+                             long long slot_stride, const int* cu_q, const int* state_slot, int n_seqs, int H, int G, int dk,
+                             int dv, int delta, int k_times_dt, int unit_qk, float unit_eps, float q_scale, int dtype,
+                             void* stream) {
+  using namespace lmsf;
+  if (n_seqs <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G || dk <= 0 || dk > 256 || dv <= 0 || H > 65535 || n_seqs > 65535)
+    LMSF_REFUSE("gated_scan: %d heads over %d q/k heads, dk=%d (up to 256), dv=%d", H, G, dk, dv);
+  if (delta && !beta) LMSF_REFUSE("gated_scan: the delta rule needs a write strength per head and token");
+  ScanArgs a{out, out_stride, q, k, v, q_stride, k_stride, v_stride, dt, dt_stride, beta, beta_stride, dt_bias, a_log, skip,
+             state, slot_stride, cu_q, state_slot, H, G, dk, dv, k_times_dt, unit_qk, unit_eps, q_scale};
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc;
+  if (dtype == LMSF_F32) rc = delta ? launch_scan<float, true>(a, n_seqs, s) : launch_scan<float, false>(a, n_seqs, s);
+  else if (dtype == LMSF_BF16) rc = delta ? launch_scan<bf16, true>(a, n_seqs, s) : launch_scan<bf16, false>(a, n_seqs, s);
+  else LMSF_REFUSE("gated_scan: unknown dtype code %d", dtype);
+  return rc;
+}
+
+// x: float32 [n, n_groups * gsize]; gate (may be null) and out: rows of `dtype`; w: float32 [wlen], wlen divides into the row.
+LMSF_API int lmsf_grouped_gated_norm(void* out, long long out_stride, const float* x, long long x_stride, const void* gate,
+                                     long long gate_stride, const float* w, int wlen, int n, int n_groups, int gsize, float eps,
+                                     int gate_silu, int gate_first, int dtype, void* stream) {
+  using namespace lmsf;
+  if (n <= 0) return 0;
+  if (n_groups <= 0 || gsize <= 0 || wlen <= 0 || !(eps > 0.f)) LMSF_REFUSE("grouped_gated_norm: %d groups of %d, eps %g", n_groups, gsize, eps);
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long teams = (long long)n * n_groups;
+  const bool block = gsize > 1024;
+  const unsigned blocks = (unsigned)(block ? teams : (teams + 3) / 4);
+#define LMSF_GO(T, B) grouped_gated_norm_kernel<T, B><<<blocks, B ? 256 : 128, 0, s>>>((T*)out, out_stride, x, x_stride, (const T*)gate, gate_stride, w, wlen, n, n_groups, gsize, eps, gate_silu, gate_first)
+  if (dtype == LMSF_F32) { if (block) LMSF_GO(float, true); else LMSF_GO(float, false); }
+  else if (dtype == LMSF_BF16) { if (block) LMSF_GO(bf16, true); else LMSF_GO(bf16, false); }
+  else LMSF_REFUSE("grouped_gated_norm: unknown dtype code %d", dtype);
+#undef LMSF_GO
+  return LMSF_LAUNCH_STATUS();
+}

@@ -2,9 +2,10 @@
 // (x <- x + scale * norm_post(branch(norm_pre(x)))), and the embedding that is normed before it enters the stream.
 //
 // One kernel does what lies between two branches:
-//   res <- res + norm(y) * w_post * layer_scale      (the branch just computed, if there is one)
+//   res <- res + norm(y) * w_post * layer_scale * m  (the branch just computed, if there is one; m: one factor for the model)
 //   res <- res + first + vec                          (what a repeated span of layers adds at its entry, if given)
-//   h    = norm(res) * w_next                         (the input of the next branch, if asked for)
+//   h    = norm(res) * w_next                         (the input of the next branch, if asked for; without w_next: h = res,
+//                                                      for blocks whose branches read the stream itself)
 // Every sum, root and product is float32; y and h have the activation type.  One block per token; the row is held
 // in registers between the passes (up to kMaxPerThread values per thread), so y and res are read once.
 #include "common.cuh"
@@ -48,7 +49,7 @@ __global__ void __launch_bounds__(kThreads) stream_norm_kernel(float* __restrict
                                                                const float* __restrict__ w_post, const float* __restrict__ ls,
                                                                const float* __restrict__ first, const float* __restrict__ vec,
                                                                T* __restrict__ h, const float* __restrict__ w_next,
-                                                               int hidden, float eps_post, float eps_next) {
+                                                               int hidden, float eps_post, float eps_next, float branch_scale) {
   __shared__ float scratch[33];
   const size_t base = (size_t)blockIdx.x * hidden;
   float v[PER][V];
@@ -84,7 +85,7 @@ __global__ void __launch_bounds__(kThreads) stream_norm_kernel(float* __restrict
         for (int e = 0; e < V; ++e) {
           float b = (v[it][e] * inv_post) * wp[e];
           if (ls != nullptr) b *= l[e];
-          r[it][e] += b;
+          r[it][e] = fmaf(branch_scale, b, r[it][e]);
         }
       }
       if (first != nullptr) {
@@ -105,6 +106,14 @@ __global__ void __launch_bounds__(kThreads) stream_norm_kernel(float* __restrict
     for (int e = 0; e < V; ++e) s2 = fmaf(r[it][e], r[it][e], s2);
   }
   if (h == nullptr) return;
+  if (w_next == nullptr) {        // the stream itself, in the activation type
+#pragma unroll
+    for (int it = 0; it < PER; ++it) {
+      const int i = (it * kThreads + threadIdx.x) * V;
+      if (i < hidden) st_vec<V>(h + base + i, r[it]);
+    }
+    return;
+  }
   s2 = block_sum(s2, scratch);
   const float inv = 1.0f / sqrtf(s2 / (float)hidden + eps_next);
 #pragma unroll
@@ -154,25 +163,32 @@ __global__ void __launch_bounds__(kThreads) embed_norm_kernel(float* __restrict_
   }
 }
 
+// res = float(x): an embedding's output becomes the float32 residual stream.
+template <typename T>
+__global__ void stream_begin_kernel(float* __restrict__ res, const T* __restrict__ x, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) res[i] = to_f32(x[i]);
+}
+
 template <typename T, int PER, int V>
 static int launch_stream(float* res, const void* y, const float* w_post, const float* ls, const float* first,
                          const float* vec, void* h, const float* w_next, int n, int hidden, float eps_post, float eps_next,
-                         cudaStream_t s) {
+                         float branch_scale, cudaStream_t s) {
   return launch_pdl(stream_norm_kernel<T, PER, V>, dim3(n), dim3(kThreads), 0, s, res, (const T*)y, w_post, ls, first, vec,
-                    (T*)h, w_next, hidden, eps_post, eps_next);
+                    (T*)h, w_next, hidden, eps_post, eps_next, branch_scale);
 }
 
 template <typename T>
 static int pick_stream(float* res, const void* y, const float* w_post, const float* ls, const float* first,
                        const float* vec, void* h, const float* w_next, int n, int hidden, float eps_post, float eps_next,
-                       cudaStream_t s) {
+                       float branch_scale, cudaStream_t s) {
   // four values per thread and access where the rows allow it (every pointer is then 8- or 16-byte aligned)
   const bool wide = hidden % 4 == 0 && ((uintptr_t)res | (uintptr_t)first | (uintptr_t)w_post | (uintptr_t)ls | (uintptr_t)vec |
                                         (uintptr_t)w_next) % 16 == 0 && ((uintptr_t)y | (uintptr_t)h) % (4 * sizeof(T)) == 0;
   const int per = ceil_div(hidden, kThreads * (wide ? 4 : 1));
 #define LMSF_CASE(P)                                                                                                          \
-  if (per <= P) return wide ? launch_stream<T, P, 4>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s) \
-                            : launch_stream<T, P, 1>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s)
+  if (per <= P) return wide ? launch_stream<T, P, 4>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, branch_scale, s) \
+                            : launch_stream<T, P, 1>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, branch_scale, s)
   LMSF_CASE(1); LMSF_CASE(2); LMSF_CASE(4); LMSF_CASE(8); LMSF_CASE(16);
   if (!wide) { LMSF_CASE(32); LMSF_CASE(64); }
 #undef LMSF_CASE
@@ -182,20 +198,20 @@ static int pick_stream(float* res, const void* y, const float* w_post, const flo
 }  // namespace lmsf
 
 // res: float32 [n, hidden].  y ([n, hidden] of `dtype`, with float32 w_post [hidden] and optional float32 ls [hidden]),
-// first (float32 [n, hidden]), vec (float32 [hidden]) and h ([n, hidden] of `dtype`, with float32 w_next) may each be null.
+// first (float32 [n, hidden]), vec (float32 [hidden]) and h ([n, hidden] of `dtype`; with float32 w_next it is the normed
+// stream, without it the stream itself) may each be null.  branch_scale multiplies the normed branch before it is added.
 LMSF_API int lmsf_stream_norm(float* res, const void* y, const float* w_post, const float* ls, const float* first,
                               const float* vec, void* h, const float* w_next, int n, int hidden, float eps_post,
-                              float eps_next, int dtype, void* stream) {
+                              float eps_next, float branch_scale, int dtype, void* stream) {
   using namespace lmsf;
   if (n <= 0) return 0;
   if (hidden <= 0 || hidden > kThreads * kMaxPerThread) LMSF_REFUSE("stream_norm: width %d is outside 1..%d", hidden, kThreads * kMaxPerThread);
   if (y != nullptr && w_post == nullptr) LMSF_REFUSE("stream_norm: a branch needs the weight of its norm");
-  if (h != nullptr && w_next == nullptr) LMSF_REFUSE("stream_norm: an output needs the weight of its norm");
-  if ((y != nullptr && !(eps_post > 0.f)) || (h != nullptr && !(eps_next > 0.f))) LMSF_REFUSE("stream_norm: eps must be positive");
+  if ((y != nullptr && !(eps_post > 0.f)) || (w_next != nullptr && !(eps_next > 0.f))) LMSF_REFUSE("stream_norm: eps must be positive");
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
-  if (dtype == LMSF_F32) rc = pick_stream<float>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s);
-  else if (dtype == LMSF_BF16) rc = pick_stream<bf16>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, s);
+  if (dtype == LMSF_F32) rc = pick_stream<float>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, branch_scale, s);
+  else if (dtype == LMSF_BF16) rc = pick_stream<bf16>(res, y, w_post, ls, first, vec, h, w_next, n, hidden, eps_post, eps_next, branch_scale, s);
   else LMSF_REFUSE("stream_norm: unknown dtype code %d", dtype);
   return rc;
 }
@@ -218,4 +234,16 @@ LMSF_API int lmsf_embed_norm(float* res, float* keep, const void* table, const i
   else if (dtype == LMSF_BF16) { LMSF_CASE(bf16, 1) LMSF_CASE(bf16, 2) LMSF_CASE(bf16, 4) LMSF_CASE(bf16, 8) LMSF_CASE(bf16, 16) LMSF_CASE(bf16, 32) LMSF_CASE(bf16, 64) }
 #undef LMSF_CASE
   LMSF_REFUSE("embed_norm: unknown dtype code %d", dtype);
+}
+
+// res: float32 [count] = x [count] of `dtype`.
+LMSF_API int lmsf_stream_begin(float* res, const void* x, long long count, int dtype, void* stream) {
+  using namespace lmsf;
+  if (count <= 0) return 0;
+  const unsigned blocks = (unsigned)((count + 255) / 256);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == LMSF_F32) stream_begin_kernel<float><<<blocks, 256, 0, s>>>(res, (const float*)x, count);
+  else if (dtype == LMSF_BF16) stream_begin_kernel<bf16><<<blocks, 256, 0, s>>>(res, (const bf16*)x, count);
+  else LMSF_REFUSE("stream_begin: unknown dtype code %d", dtype);
+  return LMSF_LAUNCH_STATUS();
 }

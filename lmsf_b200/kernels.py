@@ -203,6 +203,40 @@ def rope_cache_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[tor
     _check(rc, "rope_cache.cu", "lmsf_rope_cache")
 
 
+def qk_norm_rope_cache_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], positions: torch.Tensor,
+                             token_seq: Optional[torch.Tensor], block_table: Optional[torch.Tensor], block_size: int,
+                             cache: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rot_dim: int, is_neox: bool,
+                             n_q_heads: int, n_kv_heads: int, head_dim: int, norm_dim: int, wq: Optional[torch.Tensor],
+                             wk: Optional[torch.Tensor], eps: float, error_flag: Optional[torch.Tensor] = None):
+    """Per head: RMS norm of q and k over their first `norm_dim` values (float32 weights wq, wk [norm_dim]; None: no
+    norm), then the rotation of the first `rot_dim` values, then k and v into `cache` as `rope_cache_write` does; one
+    kernel, rounded once.  q is changed in place.  cache None: q only."""
+    n = q.shape[0]
+    for name, t, heads in (("q", q, n_q_heads), ("k", k, n_kv_heads), ("v", v, n_kv_heads)):
+        if t is None:
+            continue
+        if t.dim() != 2 or t.shape[1] != heads * head_dim or t.stride(1) != 1 or t.shape[0] != n or t.dtype != q.dtype:
+            raise KernelError(f"qk_norm_rope: {name} must be [n, {heads * head_dim}] with a contiguous last dimension, of one dtype")
+    page_stride = max_blocks = 0
+    if cache is not None:
+        if cache.dtype != q.dtype or not cache.is_contiguous() or tuple(cache.shape[1:]) != (2, n_kv_heads, block_size, head_dim):
+            raise KernelError(f"qk_norm_rope: cache of shape {tuple(cache.shape)} does not match "
+                              f"[pages, 2, {n_kv_heads}, {block_size}, {head_dim}] of {q.dtype}")
+        page_stride, max_blocks = cache.stride(0), block_table.shape[1]
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dim // 2):
+        raise KernelError("qk_norm_rope: inv_freq must hold rot_dim / 2 float32 values")
+    f = _func("qk_norm_rope.cu", "lmsf_qk_norm_rope_cache_write",
+              [c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+               c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+               c_float, c_int, c_void_p, c_void_p])
+    rc = f(_ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0) if k is not None else 0,
+           v.stride(0) if v is not None else 0, _i32(positions, "positions"), _i32(token_seq, "token_seq"),
+           _i32(block_table, "block_table"), max_blocks, block_size, _ptr(cache), page_stride, _ptr(inv_freq),
+           rot_dim, int(is_neox), n, n_q_heads, n_kv_heads, head_dim, norm_dim, _f32vec(wq, norm_dim, "wq"),
+           _f32vec(wk, norm_dim, "wk"), float(eps), dtype_code(q.dtype), _i32(error_flag, "error_flag"), _stream())
+    _check(rc, "qk_norm_rope.cu", "lmsf_qk_norm_rope")
+
+
 # ----------------------------------------------------------------------------- attention (generic)
 
 GENERIC_MAX_HEAD_DIM = 512     # the plain attention kernel holds a head's accumulator in registers up to this size
@@ -248,6 +282,40 @@ def gated_act(out: torch.Tensor, x: torch.Tensor, act: str = "silu"):
         raise KernelError(f"gated_act: unknown activation {act!r} (known: {', '.join(sorted(ACT_CODES))})")
     f = _func("activation.cu", "lmsf_gated_act", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_void_p])
     rc = f(_ptr(out), _ptr(x), n, d, x.stride(0), ACT_CODES[act], dtype_code(out.dtype), _stream())
+    _check(rc, "activation.cu", "lmsf_activation")
+
+
+def clamped_glu(out: torch.Tensor, x: torch.Tensor, limit: float, alpha: float = 1.702):
+    """out[t, i] = g * sigmoid(alpha * g) * (u + 1) with g = min(x[t, i], limit), u = clamp(x[t, d + i], -limit, limit);
+    x: [n, 2 d], out: [n, d] contiguous."""
+    n, d = out.shape
+    if x.shape != (n, 2 * d) or x.stride(1) != 1 or not out.is_contiguous() or x.dtype != out.dtype:
+        raise KernelError("clamped_glu: x must be [n, 2d] and out [n, d] of one dtype")
+    f = _func("activation.cu", "lmsf_clamped_glu", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_float, c_float, c_int, c_void_p])
+    rc = f(_ptr(out), _ptr(x), n, d, x.stride(0), float(limit), float(alpha), dtype_code(out.dtype), _stream())
+    _check(rc, "activation.cu", "lmsf_activation")
+
+
+def gelu_mul_gather(out: torch.Tensor, a: torch.Tensor, table: torch.Tensor, offset: int, ids: torch.Tensor,
+                    error_flag: Optional[torch.Tensor] = None):
+    """out[t, i] = gelu_tanh(a[t, i]) * table[ids[t], offset + i]; a: [n, d] view, table: [vocab, width] contiguous."""
+    n, d = out.shape
+    if a.shape != (n, d) or a.stride(1) != 1 or not out.is_contiguous() or a.dtype != out.dtype or table.dtype != out.dtype \
+            or table.dim() != 2 or not table.is_contiguous():
+        raise KernelError("gelu_mul_gather: a and out [n, d] and a contiguous table [vocab, width] of one dtype")
+    f = _func("activation.cu", "lmsf_gelu_mul_gather",
+              [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    rc = f(_ptr(out), _ptr(a), a.stride(0), _ptr(table), table.shape[1], int(offset), _i32(ids, "ids"), table.shape[0], n, d,
+           dtype_code(out.dtype), _i32(error_flag, "error_flag"), _stream())
+    _check(rc, "activation.cu", "lmsf_activation")
+
+
+def scale_softcap_(x: torch.Tensor, scale: float = 1.0, cap: float = 0.0):
+    """x <- cap * tanh(x * scale / cap) in place (cap 0: x * scale); x: contiguous float32."""
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale_softcap: x must be contiguous float32")
+    f = _func("activation.cu", "lmsf_scale_softcap", [c_void_p, c_longlong, c_float, c_float, c_void_p])
+    rc = f(_ptr(x), x.numel(), float(scale), float(cap or 0.0), _stream())
     _check(rc, "activation.cu", "lmsf_activation")
 
 
@@ -719,9 +787,10 @@ def _f32vec(t: Optional[torch.Tensor], n: int, name: str) -> Optional[int]:
 def stream_norm(res: torch.Tensor, y: Optional[torch.Tensor] = None, w_post: Optional[torch.Tensor] = None,
                 layer_scale: Optional[torch.Tensor] = None, eps_post: float = 0.0, first: Optional[torch.Tensor] = None,
                 vec: Optional[torch.Tensor] = None, h: Optional[torch.Tensor] = None, w_next: Optional[torch.Tensor] = None,
-                eps_next: float = 0.0):
+                eps_next: float = 0.0, branch_scale: float = 1.0):
     """What lies between two branches of a block that norms a branch before and after it, in one kernel, float32 inside:
-    res += norm(y) * w_post * layer_scale (if y); res += first + vec (whichever is given); h = norm(res) * w_next (if h).
+    res += branch_scale * norm(y) * w_post * layer_scale (if y); res += first + vec (whichever is given);
+    h = norm(res) * w_next (if h; without w_next h is the stream itself in the activation type).
     res, first: float32 [n, hidden]; y, h: [n, hidden] of the activation type; the vectors are float32 [hidden]."""
     n, hidden = res.shape
     if res.dtype != torch.float32 or not res.is_contiguous():
@@ -736,10 +805,19 @@ def stream_norm(res: torch.Tensor, y: Optional[torch.Tensor] = None, w_post: Opt
         return
     f = _func("stream_norm.cu", "lmsf_stream_norm",
               [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
-               c_float, c_int, c_void_p])
+               c_float, c_float, c_int, c_void_p])
     rc = f(_ptr(res), _ptr(y), _f32vec(w_post, hidden, "w_post"), _f32vec(layer_scale, hidden, "layer_scale"), _ptr(first),
            _f32vec(vec, hidden, "vec"), _ptr(h), _f32vec(w_next, hidden, "w_next"), n, hidden, float(eps_post),
-           float(eps_next), dtype_code(act.dtype) if act is not None else F32, _stream())
+           float(eps_next), float(branch_scale), dtype_code(act.dtype) if act is not None else F32, _stream())
+    _check(rc, "stream_norm.cu", "lmsf_stream_norm")
+
+
+def stream_begin(res: torch.Tensor, x: torch.Tensor):
+    """res = float(x): an embedding's output becomes the float32 residual stream."""
+    if res.dtype != torch.float32 or res.shape != x.shape or not (res.is_contiguous() and x.is_contiguous()):
+        raise KernelError("stream_begin: res must be contiguous float32 of x's shape")
+    f = _func("stream_norm.cu", "lmsf_stream_begin", [c_void_p, c_void_p, c_longlong, c_int, c_void_p])
+    rc = f(_ptr(res), _ptr(x), x.numel(), dtype_code(x.dtype), _stream())
     _check(rc, "stream_norm.cu", "lmsf_stream_norm")
 
 
@@ -828,6 +906,95 @@ def gated_norm(out: torch.Tensor, x: torch.Tensor, gate: torch.Tensor, w: torch.
     rc = f(_ptr(out), _ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _f32vec(w, width, "w"), n, width, float(eps),
            dtype_code(out.dtype), _stream())
     _check(rc, "lightning.cu", "lmsf_lightning")
+
+
+# ----------------------------------------------------------------------------- recurrent mixers with a state matrix per head
+
+CONV_MAX_TAPS = 8
+SCAN_MAX_DK = 256
+
+
+def _rows(t: torch.Tensor, width: int, name: str, dtype: Optional[torch.dtype] = None):
+    if t.dim() != 2 or t.shape[1] != width or t.stride(1) != 1 or (dtype is not None and t.dtype != dtype):
+        raise KernelError(f"{name} must be [n, {width}] with a contiguous last dimension" + (f" of {dtype}" if dtype else ""))
+
+
+def causal_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+                state_offset: int, cu_q: torch.Tensor, state_slot: torch.Tensor, n_seqs: int, max_q: int, act: str = "silu"):
+    """out[t, c] = act(bias[c] + sum_j w[c, j] x[t - (taps - 1) + j, c]) per request (tokens cu_q[s]..cu_q[s + 1]); the
+    inputs before a portion come from state[slot, state_offset : state_offset + (taps - 1) * C] ([taps - 1, C], float32),
+    which then takes the portion's last inputs.  x, out: [n, C] views; w: float32 [C, taps]; state: float32 [slots, size]."""
+    n, C = x.shape
+    taps = w.shape[1]
+    _rows(x, C, "causal_conv: x")
+    _rows(out, C, "causal_conv: out", x.dtype)
+    if out.shape[0] != n or w.dtype != torch.float32 or w.shape != (C, taps) or not w.is_contiguous():
+        raise KernelError("causal_conv: w must be contiguous float32 [channels, taps]")
+    if state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous() or \
+            state_offset < 0 or state_offset + (taps - 1) * C > state.shape[1]:
+        raise KernelError("causal_conv: the state must be contiguous float32 [slots, size] with room for [taps - 1, channels]")
+    f = _func("recurrent.cu", "lmsf_causal_conv",
+              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
+               c_int, c_int, c_int, c_int, c_int, c_void_p])
+    rc = f(_ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(w), _f32vec(bias, C, "bias"),
+           state.data_ptr() + 4 * state_offset, state.stride(0), _i32(cu_q, "cu_q"), _i32(state_slot, "state_slot"), n_seqs,
+           int(max_q), C, taps, {"none": 0, None: 0, "silu": 1}[act], dtype_code(x.dtype), _stream())
+    _check(rc, "recurrent.cu", "lmsf_recurrent")
+
+
+def gated_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dt: torch.Tensor,
+               beta: Optional[torch.Tensor], dt_bias: torch.Tensor, a_log: torch.Tensor, skip: Optional[torch.Tensor],
+               state: torch.Tensor, cu_q: torch.Tensor, state_slot: torch.Tensor, n_seqs: int, heads: int, qk_heads: int,
+               dk: int, dv: int, delta: bool, k_times_dt: bool = False, unit_qk: bool = False, unit_eps: float = 1e-6,
+               q_scale: float = 1.0):
+    """Per request, head h and token: step = softplus(dt[t, h] + dt_bias[h]), a = exp(-exp(a_log[h]) * step);
+    plain rule: S = a S + (step k) v^T (k v^T without k_times_dt); delta rule: S = a S, u = sigmoid(beta[t, h]) (v - S^T k),
+    S += k u^T; out[t, h] = S^T q + skip[h] v.  Head h reads q/k head h // (heads / qk_heads); unit_qk makes q and k unit
+    vectors first (x / sqrt(sum x^2 + unit_eps)) and multiplies q by q_scale.  S = the first heads * dv * dk values of
+    state[slot] (float32 [slots, size], stored [head][dv][dk]), read before and written after.
+    q, k: [n, qk_heads * dk]; v: [n, heads * dv]; dt, beta: [n, heads] (views of one dtype); out: float32 [n, heads * dv]."""
+    n = q.shape[0]
+    _rows(q, qk_heads * dk, "gated_scan: q")
+    _rows(k, qk_heads * dk, "gated_scan: k", q.dtype)
+    _rows(v, heads * dv, "gated_scan: v", q.dtype)
+    _rows(dt, heads, "gated_scan: dt", q.dtype)
+    if beta is not None:
+        _rows(beta, heads, "gated_scan: beta", q.dtype)
+    _rows(out, heads * dv, "gated_scan: out", torch.float32)
+    if state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous() or state.shape[1] < heads * dv * dk:
+        raise KernelError("gated_scan: the state must be contiguous float32 [slots, >= heads * dv * dk]")
+    f = _func("recurrent.cu", "lmsf_gated_scan",
+              [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_longlong,
+               c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int,
+               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+    rc = f(_ptr(out), out.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(dt), dt.stride(0),
+           _ptr(beta), beta.stride(0) if beta is not None else 0, _f32vec(dt_bias, heads, "dt_bias"),
+           _f32vec(a_log, heads, "a_log"), _f32vec(skip, heads, "skip"), _ptr(state), state.stride(0), _i32(cu_q, "cu_q"),
+           _i32(state_slot, "state_slot"), n_seqs, heads, qk_heads, dk, dv, int(delta), int(k_times_dt), int(unit_qk),
+           float(unit_eps), float(q_scale), dtype_code(q.dtype), _stream())
+    _check(rc, "recurrent.cu", "lmsf_recurrent")
+
+
+def grouped_gated_norm(out: torch.Tensor, x: torch.Tensor, gate: Optional[torch.Tensor], w: torch.Tensor, group_size: int,
+                       eps: float, gate_act: str = "silu", gate_first: bool = False):
+    """Per group of `group_size` columns: out = x / rms(x) * w * act(gate), or with gate_first out = y / rms(y) * w for
+    y = x * act(gate).  x: float32 [n, width]; gate, out: [n, width] views of the activation type; w: float32, its length
+    divides into a row (a weight shorter than the row is shared by the groups)."""
+    n, width = x.shape
+    _rows(x, width, "grouped_gated_norm: x", torch.float32)
+    _rows(out, width, "grouped_gated_norm: out")
+    if gate is not None:
+        _rows(gate, width, "grouped_gated_norm: gate", out.dtype)
+    if width % group_size or w.dtype != torch.float32 or w.dim() != 1 or not w.is_contiguous() or width % w.numel() \
+            or (w.numel() % group_size and group_size % w.numel()):
+        raise KernelError("grouped_gated_norm: the groups and the weight must divide a row")
+    f = _func("recurrent.cu", "lmsf_grouped_gated_norm",
+              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_float,
+               c_int, c_int, c_int, c_void_p])
+    rc = f(_ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(w),
+           w.numel(), n, width // group_size, group_size, float(eps), int(gate_act == "silu"), int(gate_first),
+           dtype_code(out.dtype), _stream())
+    _check(rc, "recurrent.cu", "lmsf_recurrent")
 
 
 # ----------------------------------------------------------------------------- attention over a cached low-rank vector
@@ -953,6 +1120,23 @@ def moe_topk(ids: torch.Tensor, wts: torch.Tensor, logits: torch.Tensor, bias: O
         raise KernelError("moe: one float32 weight per choice")
     f = _func("moe.cu", "lmsf_moe_topk", [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
     rc = f(_ptr(logits), logits.stride(0), _f32vec(bias, experts, "bias"), n, experts, top, _i32(ids, "ids"), _ptr(wts), _stream())
+    _check(rc, "moe.cu", "lmsf_moe")
+
+
+def moe_topk_sigmoid(ids: torch.Tensor, wts: torch.Tensor, logits: torch.Tensor, correction: Optional[torch.Tensor],
+                     experts: int, n_groups: int = 1, keep: int = 1, weight_scale: float = 1.0):
+    """ids, wts [n, top]: scores s = sigmoid(logits[t, :experts]); the `top` largest s + correction among the experts
+    of the `keep` best of `n_groups` groups of neighbours (a group's score: the sum of its two largest s + correction);
+    the weights are the chosen s times weight_scale, not renormalised."""
+    n, top = ids.shape
+    if logits.dtype != torch.float32 or logits.shape[0] != n or logits.shape[1] < experts or logits.stride(1) != 1:
+        raise KernelError("moe: the router's logits must be float32 [n, >= experts]")
+    if wts.dtype != torch.float32 or wts.shape != ids.shape or not wts.is_contiguous():
+        raise KernelError("moe: one float32 weight per choice")
+    f = _func("moe.cu", "lmsf_moe_topk_sigmoid",
+              [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p])
+    rc = f(_ptr(logits), logits.stride(0), _f32vec(correction, experts, "correction"), n, experts, top, int(n_groups), int(keep),
+           float(weight_scale), _i32(ids, "ids"), _ptr(wts), _stream())
     _check(rc, "moe.cu", "lmsf_moe")
 
 

@@ -2,5 +2,5 @@
 from .base import (Block, CacheGroupView, FeedForward, KVCacheSpec, LayerCache, LayerCall, LayerSpec, Mixer, ModelSpec,
                    Norm, Part, PartSpec, PositionEncoding, StateSpec, StepContext, WeightSpec, build_part, part_class,
                    register_part)
-from . import (attention, block, embedding, latent_attention, lightning, linear, mlp, moe, norm, rope,  # noqa: F401
-               stream_entry)  # (registration)
+from . import (attention, block, embedding, latent_attention, lightning, linear, mlp, moe, norm, recurrent, rope,  # noqa: F401
+               stream_entry, token_gate)  # (registration)

@@ -36,13 +36,28 @@ class PagedAttention(Mixer):
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: Optional[PositionEncoding] = None, window: Optional[int] = None,
-                 scale: Optional[float] = None, bias: bool = False, softcap: Optional[float] = None):
+                 scale: Optional[float] = None, bias: bool = False, softcap: Optional[float] = None,
+                 value_dim: Optional[int] = None, qk_norm: bool = False, qk_norm_eps: float = 1e-6):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads cannot be grouped over {num_kv_heads} kv heads")
-        if head_dim % 16 or not (16 <= head_dim <= 256):
+        # head_dim is the stored size of a query or key head, value_dim that of a value head (default: the same).  The
+        # cache and the kernels work on ONE width per head, a multiple of 16; where the stored sizes differ from it the
+        # weights are padded with zero rows and columns when they are set (zeros change neither scores nor outputs)
+        self.qk_dim, self.value_dim = int(head_dim), int(value_dim or head_dim)
+        padded = value_dim is not None or qk_norm
+        width = (max(self.qk_dim, self.value_dim) + 15) // 16 * 16 if padded else head_dim
+        if width % 16 or not (16 <= width <= 256):
             raise ValueError(f"head_dim {head_dim} is not supported: the attention kernels take multiples of 16 "
                              f"from 16 to 256")
+        scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+        head_dim = width
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
+        # RMS norm of every query and key head before the rotation (weights q_norm, k_norm [qk_dim], shared by the heads)
+        self.qk_norm, self.qk_norm_eps = bool(qk_norm), float(qk_norm_eps)
+        self.q_norm: Optional[torch.Tensor] = None
+        self.k_norm: Optional[torch.Tensor] = None
+        self._qn32: Optional[torch.Tensor] = None
+        self._kn32: Optional[torch.Tensor] = None
         self.position_encoding = position_encoding
         self.window = int(window) if window else None
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
@@ -58,13 +73,39 @@ class PagedAttention(Mixer):
         self.o_bias: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        specs = {"qkv": WeightSpec([(self.q_size, self.hidden_size), (self.kv_size, self.hidden_size),
-                                    (self.kv_size, self.hidden_size)]),
-                 "o": WeightSpec([(self.hidden_size, self.q_size)])}
+        H, G, dk, dv, D = self.num_heads, self.num_kv_heads, self.qk_dim, self.value_dim, self.hidden_size
+        specs = {"qkv": WeightSpec([(H * dk, D), (G * dk, D), (G * dv, D)]),
+                 "o": WeightSpec([(D, H * dv)])}
         if self.has_bias:
-            specs["qkv_bias"] = WeightSpec([(self.q_size,), (self.kv_size,), (self.kv_size,)])
-            specs["o_bias"] = WeightSpec([(self.hidden_size,)])
+            specs["qkv_bias"] = WeightSpec([(H * dk,), (G * dk,), (G * dv,)])
+            specs["o_bias"] = WeightSpec([(D,)])
+        if self.qk_norm:
+            specs["q_norm"] = WeightSpec([(dk,)], keep_fp32=True)
+            specs["k_norm"] = WeightSpec([(dk,)], keep_fp32=True)
         return specs
+
+    def set_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        H, G, dk, dv, hd = self.num_heads, self.num_kv_heads, self.qk_dim, self.value_dim, self.head_dim
+        if dk != hd or dv != hd:
+            tensors = dict(tensors)
+
+            def pad_heads(t, heads, size):           # rows [heads * size, ...] -> [heads * hd, ...], zeros after `size`
+                t = t.reshape(heads, size, *t.shape[1:])
+                out = t.new_zeros((heads, hd, *t.shape[2:]))
+                out[:, :size] = t
+                return out.reshape(heads * hd, *t.shape[2:])
+
+            for name in ("qkv", "qkv_bias"):
+                if name in tensors:
+                    t = tensors[name]
+                    q, k, v = t[:H * dk], t[H * dk:(H + G) * dk], t[(H + G) * dk:]
+                    tensors[name] = torch.cat([pad_heads(q, H, dk), pad_heads(k, G, dk), pad_heads(v, G, dv)], 0).contiguous()
+            if "o" in tensors:
+                o = tensors["o"].reshape(-1, H, dv)
+                po = o.new_zeros((o.shape[0], H, hd))
+                po[:, :, :dv] = o
+                tensors["o"] = po.reshape(o.shape[0], H * hd).contiguous()
+        super().set_weights(tensors)
 
     def cache_spec(self) -> Optional[KVCacheSpec]:
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
@@ -75,6 +116,8 @@ class PagedAttention(Mixer):
     def prepare(self, dtype, device) -> None:
         if self.position_encoding is not None:
             self.position_encoding.prepare(dtype, device)
+        if self.qk_norm:
+            self._qn32, self._kn32 = self.q_norm.float().contiguous(), self.k_norm.float().contiguous()
         if dtype == torch.bfloat16 and not kernels.mma_attention_supported(dtype, self.head_dim):
             # right but slow: said once, so that nobody wonders where the time goes
             warnings.warn(f"head_dim {self.head_dim} is beyond the tensor-core attention kernels "
@@ -94,7 +137,7 @@ class PagedAttention(Mixer):
         group = ctx.groups[cache.group]
         fused = self.position_encoding.fused_rotary() if self.position_encoding is not None else None
         hx = h.x if isinstance(h, Prenormed) else h
-        if (FUSE_QKV_ROPE and cache.owner and linear.USE_SKINNY and self.qkv_bias is None and (fused is not None or self.position_encoding is None)
+        if (FUSE_QKV_ROPE and cache.owner and linear.USE_SKINNY and self.qkv_bias is None and not self.qk_norm and (fused is not None or self.position_encoding is None)
                 and kernels.gemm_skinny_qkv_rope_supported(hx, self.qkv, self.head_dim, fused[1] if fused else 0,
                                                            fused[2] if fused else True)):
             # a few single tokens (a decode step): projection, rotation and cache write in one kernel
@@ -116,9 +159,17 @@ class PagedAttention(Mixer):
             q = matmul_tn(h, self.qkv[:self.q_size], bias=None if self.qkv_bias is None else self.qkv_bias[:self.q_size])
             k = v = None
         if self.position_encoding is not None and fused is None:
+            if self.qk_norm:
+                raise ValueError("a norm of queries and keys goes with a rotary encoding or none")
             self.position_encoding.apply(ctx, q, k, self.num_heads, self.num_kv_heads, self.head_dim)
         inv_freq, rot_dim, is_neox = fused if fused is not None else (None, 0, True)
-        if fused is not None or cache.owner:
+        if self.qk_norm:
+            # norm, rotation and cache write in one kernel; the value is rounded once
+            kernels.qk_norm_rope_cache_write(q, k, v, ctx.positions, ctx.token_seq, group.block_table, group.block_size,
+                                             cache.kv if cache.owner else None, inv_freq, rot_dim, is_neox, self.num_heads,
+                                             self.num_kv_heads, self.head_dim, self.qk_dim, self._qn32, self._kn32,
+                                             self.qk_norm_eps, ctx.error_flag)
+        elif fused is not None or cache.owner:
             kernels.rope_cache_write(q, k, v, ctx.positions, ctx.token_seq, group.block_table, group.block_size,
                                      cache.kv if cache.owner else None, inv_freq, rot_dim, is_neox, self.num_heads,
                                      self.num_kv_heads, self.head_dim, ctx.error_flag)

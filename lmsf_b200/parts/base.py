@@ -223,9 +223,10 @@ class Prenormed:
 @dataclass
 class Normed:
     """The residual stream `res` holds every branch so far and `h` is already `norm` of it: what a block returns as
-    x when it has applied the next block's first norm itself (or None as x: nothing is pending, no norm applied)."""
+    x when it has applied the next block's first norm itself (or None as x: nothing is pending, no norm applied).
+    `norm` None: the next block's branches read the stream itself, and `h` is the stream in the activation type."""
     h: torch.Tensor
-    norm: Norm
+    norm: Optional[Norm]
     res: torch.Tensor
 
 

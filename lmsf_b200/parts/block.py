@@ -103,3 +103,71 @@ class SandwichNormBlock(Block):
         f = self.feed_forward.forward(ctx, h)
         h = self._between(res, f, self.ffn_post, nxt)
         return (Normed(h, nxt, res) if nxt is not None else None), res
+
+
+@register_part("block", "branch_norm")
+class BranchNormBlock(Block):
+    """Norms on the branches' outputs only:  x <- x + m * norm(mixer(x)),  x <- x + m * norm(ff(x)), and, where the layer
+    has one, a third branch after the feed-forward, x <- x + m * norm(side(x)).  The branches read the stream itself (in
+    the activation type); m is one factor for the whole model.  The residual stream is float32 and every sum into it is
+    made in float32 from the float32 normed branch.  One kernel does what lies between two branches: the norm of the
+    branch before, the scaled add, and the stream in the activation type for the branch after (`kernels.stream_norm`
+    without a next norm); with `next_entry` of a block of this kind the last of them also serves the next block."""
+    ROLES = {"mixer": "mixer", "mixer_post_norm": "norm", "feed_forward": "feed_forward", "ffn_post_norm": "norm",
+             "side": "feed_forward", "side_post_norm": "norm"}
+    OPTIONAL_ROLES = ("feed_forward", "ffn_post_norm", "side", "side_post_norm")
+    fuses_next_norm = True
+
+    def __init__(self, parts: Dict[str, Part], residual_mult: float = 1.0):
+        super().__init__(parts)
+        self.residual_mult = float(residual_mult)
+        self._mixer = parts["mixer"]
+        self.branches = [(parts["mixer"], parts["mixer_post_norm"])]
+        for role, norm in (("feed_forward", "ffn_post_norm"), ("side", "side_post_norm")):
+            if role in parts:
+                if norm not in parts:
+                    raise ValueError(f"the branch {role!r} needs its norm {norm!r}")
+                self.branches.append((parts[role], parts[norm]))
+        for _, n in self.branches:
+            if not hasattr(n, "weight_f32") or getattr(n, "has_layer_scale", False):
+                raise ValueError("the branch-norm block takes norms that are a factor per row times a weight (rmsnorm)")
+
+    def entry(self) -> Optional[Tuple[Norm, Part]]:
+        return None, self._mixer          # no norm before the first branch: it wants the stream itself
+
+    def forward(self, ctx: StepContext, x, res: Optional[torch.Tensor], cache: LayerCache,
+                next_entry: Optional[Tuple[Norm, Part]] = None):
+        if isinstance(x, Normed):             # the block before left the stream in the activation type
+            if x.norm is not None or x.res is not res:
+                raise ValueError("a prepared activation was made for another norm or residual stream")
+            h = x.h
+        elif x is None:                       # a complete float32 stream
+            h = self._as_activation(ctx, res)
+        elif res is None:                     # the embedding's output starts the stream
+            h = x
+            if x.dtype == torch.float32:
+                res = x
+            else:
+                res = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+                kernels.stream_begin(res, x)
+        else:
+            raise ValueError("the branch-norm block takes a complete stream, not a pending branch")
+        wants_stream = next_entry is not None and next_entry[0] is None
+        for i, (part, norm) in enumerate(self.branches):
+            y = part.forward(ctx, h, cache) if i == 0 else part.forward(ctx, h)
+            last = i == len(self.branches) - 1
+            need_h = (not last) or wants_stream
+            h = torch.empty_like(y) if (need_h and ctx.dtype != torch.float32) else None
+            kernels.stream_norm(res, y=y, w_post=norm.weight_f32(), eps_post=norm.eps, h=h,
+                                branch_scale=self.residual_mult)
+            if need_h and h is None:
+                h = res                       # float32 activations: the stream itself (no part writes its input)
+        return (Normed(h, None, res) if wants_stream else None), res
+
+    @staticmethod
+    def _as_activation(ctx: StepContext, res: torch.Tensor) -> torch.Tensor:
+        if ctx.dtype == torch.float32:
+            return res
+        h = torch.empty(res.shape, dtype=ctx.dtype, device=res.device)
+        kernels.stream_norm(res, h=h)
+        return h

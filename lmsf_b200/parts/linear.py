@@ -110,7 +110,9 @@ class Linear(Part):
     graph_safe = True
 
     def __init__(self, in_features: int, out_features: Union[int, Sequence[int]], out_dtype: Optional[str] = None,
-                 bias: bool = False):
+                 bias: bool = False, out_scale: float = 1.0, out_softcap: Optional[float] = None):
+        # an output head may scale its float32 results and cap them smoothly: cap * tanh(scale * y / cap)
+        self.out_scale, self.out_softcap = float(out_scale), float(out_softcap or 0.0)
         self.in_features = int(in_features)
         self.has_bias = bool(bias)
         self.bias: Optional[torch.Tensor] = None
@@ -126,4 +128,9 @@ class Linear(Part):
         return specs
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return matmul_tn(x, self.weight, self.out_dtype, self.bias)
+        y = matmul_tn(x, self.weight, self.out_dtype, self.bias)
+        if self.out_scale != 1.0 or self.out_softcap:
+            if y.dtype != torch.float32:
+                raise ValueError("a scaled or capped output is float32 (out_dtype='float32')")
+            kernels.scale_softcap_(y, self.out_scale, self.out_softcap)
+        return y

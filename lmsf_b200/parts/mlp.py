@@ -3,6 +3,9 @@
 Reference: Mlp in core/src/model_executor/models/llama/llama.rs:223-274 with silu_and_mul_kernel
 (vllm/kernels/activation_kernels.cu:26-41).  The activation is a parameter here (the reference
 fixes SiLU in code although it parses `hidden_act`).
+
+A second form, `clamped_swiglu`, clamps both factors first: g = min(gate, limit), u = clamp(up, -limit, limit),
+product g * sigmoid(alpha * g) * (u + 1); `limit` and `alpha` are parameters.
 """
 from __future__ import annotations
 
@@ -22,10 +25,15 @@ class GatedMLP(FeedForward):
     takes_prenormed = True
     fuses_norm = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False):
-        if activation not in kernels.ACT_CODES:
-            raise ValueError(f"activation {activation!r} is not supported (known: {', '.join(sorted(kernels.ACT_CODES))})")
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False,
+                 limit: Optional[float] = None, alpha: float = 1.702):
+        if activation not in kernels.ACT_CODES and activation != "clamped_swiglu":
+            raise ValueError(f"activation {activation!r} is not supported (known: clamped_swiglu, "
+                             f"{', '.join(sorted(kernels.ACT_CODES))})")
+        if activation == "clamped_swiglu" and not (limit is not None and limit > 0):
+            raise ValueError("the clamped activation needs a positive limit")
         self.hidden_size, self.intermediate_size, self.activation = int(hidden_size), int(intermediate_size), activation
+        self.limit, self.alpha = (float(limit) if limit is not None else None), float(alpha)
         self.has_bias = bool(bias)
         self.gate_up: Optional[torch.Tensor] = None
         self.down: Optional[torch.Tensor] = None
@@ -45,7 +53,8 @@ class GatedMLP(FeedForward):
 
     def forward(self, ctx: StepContext, h, then: Optional[NormAfter] = None):
         hx = h.x if isinstance(h, Prenormed) else h
-        if linear.USE_SKINNY and self.gate_up_bias is None and kernels.gemm_skinny_supported(hx, self.gate_up):
+        if linear.USE_SKINNY and self.gate_up_bias is None and self.activation in kernels.ACT_CODES and \
+                kernels.gemm_skinny_supported(hx, self.gate_up):
             # a decode step: gate, up and the activation in one pass over the weights
             m = torch.empty((hx.shape[0], self.intermediate_size), dtype=hx.dtype, device=hx.device)
             kernels.gemm_skinny(m, hx, self.gate_up, fuse_act=self.activation,
@@ -53,7 +62,10 @@ class GatedMLP(FeedForward):
             return self._down(m, then)
         gu = matmul_tn(h, self.gate_up, bias=self.gate_up_bias)
         m = torch.empty((gu.shape[0], self.intermediate_size), dtype=gu.dtype, device=gu.device)
-        kernels.gated_act(m, gu, self.activation)
+        if self.activation == "clamped_swiglu":
+            kernels.clamped_glu(m, gu, self.limit, self.alpha)
+        else:
+            kernels.gated_act(m, gu, self.activation)
         return self._down(m, then)
 
     def _down(self, m: torch.Tensor, then: Optional[NormAfter]):

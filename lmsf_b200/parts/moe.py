@@ -4,6 +4,11 @@
   out = sum_j weight_j * expert_(e_j)(h)  +  sigmoid(h ws^T) * shared(h)
   expert(h) = act(h Wup^T) Wdown^T,  act = the square of relu (no gate matrix, no biases)
 
+A second form of both halves, by parameters: `routing="sigmoid_groups"` scores the experts by s = sigmoid(z), chooses by
+s + correction among the experts of the `group_keep` best of `groups` groups of neighbours (a group's score: the sum of its
+two largest s + correction) and weighs by the chosen s themselves; `activation="clamped_swiglu"` gives every expert a gate
+and an up matrix: g = min(gate h, limit), u = clamp(up h, -limit, limit), expert(h) = (g sigmoid(alpha g) (u + 1)) Wdown^T.
+
 All experts' matrices are stacked ([experts, ff, width], [experts, width, ff]).  The routing is sorted on the device
 (csrc/moe.cu): no value comes back to the host, and a step's launches have the same shape whatever the routing is, so
 decode steps can be replayed from CUDA graphs.  The router and the shared expert's gate are rows of one float32 product.
@@ -27,11 +32,25 @@ class RoutedExperts(FeedForward):
     graph_safe = True
 
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, expert_size: int, shared_size: int = 0,
-                 activation: str = "relu2", router_bias: bool = True, shared_gate: bool = True):
+                 activation: str = "relu2", router_bias: bool = True, shared_gate: bool = True,
+                 routing: str = "softmax_top", groups: int = 1, group_keep: int = 1, limit: Optional[float] = None,
+                 alpha: float = 1.702):
         if not (0 < top_k <= num_experts):
             raise ValueError(f"{top_k} choices of {num_experts} experts")
-        if activation not in kernels.MOE_ACTS:
-            raise ValueError(f"activation {activation!r} is not supported (known: relu2, none)")
+        if activation not in kernels.MOE_ACTS and activation != "clamped_swiglu":
+            raise ValueError(f"activation {activation!r} is not supported (known: relu2, clamped_swiglu, none)")
+        if routing not in ("softmax_top", "sigmoid_groups"):
+            raise ValueError(f"routing {routing!r} is not supported (known: softmax_top, sigmoid_groups)")
+        self.routing, self.groups, self.group_keep = routing, int(groups), int(group_keep)
+        if routing == "sigmoid_groups" and (self.groups < 1 or num_experts % self.groups or not (1 <= self.group_keep <= self.groups)
+                                            or self.group_keep * (num_experts // self.groups) < top_k):
+            raise ValueError(f"{num_experts} experts in {groups} groups of which {group_keep} are kept cannot give {top_k} choices")
+        self.gated = activation == "clamped_swiglu"        # experts with a gate and an up matrix
+        if self.gated and not (limit is not None and limit > 0):
+            raise ValueError("the clamped activation needs a positive limit")
+        if self.gated and shared_size:
+            raise ValueError("a shared expert with the clamped activation is not built")
+        self.limit, self.alpha = (float(limit) if limit is not None else None), float(alpha)
         self.hidden_size, self.num_experts, self.top_k = int(hidden_size), int(num_experts), int(top_k)
         self.expert_size, self.shared_size = int(expert_size), int(shared_size or 0)
         self.activation = activation
@@ -47,7 +66,8 @@ class RoutedExperts(FeedForward):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         D, E, F = self.hidden_size, self.num_experts, self.expert_size
-        specs = {"up": WeightSpec([(F, D)] * E), "down": WeightSpec([(D, F)] * E),
+        # gated experts: "up" lists, expert by expert, the gate matrix and then the up matrix
+        specs = {"up": WeightSpec([(F, D)] * (2 * E if self.gated else E)), "down": WeightSpec([(D, F)] * E),
                  "router": WeightSpec([(E, D)] + ([(1, D)] if self.has_shared_gate else []))}
         if self.has_router_bias:
             specs["router_bias"] = WeightSpec([(E,)], keep_fp32=True)
@@ -57,7 +77,7 @@ class RoutedExperts(FeedForward):
         return specs
 
     def activation_width(self) -> int:
-        return self.top_k * (self.expert_size + 2 * self.hidden_size) + self.shared_size + self.hidden_size
+        return self.top_k * ((3 if self.gated else 1) * self.expert_size + 2 * self.hidden_size) + self.shared_size + self.hidden_size
 
     def prepare(self, dtype, device) -> None:
         self._bias32 = self.router_bias.float().contiguous() if self.has_router_bias else None
@@ -68,9 +88,14 @@ class RoutedExperts(FeedForward):
         z = matmul_tn(h, self.router, out_dtype=torch.float32)           # [n, experts (+ 1: the shared expert's gate)]
         ids = torch.empty((n, K), dtype=torch.int32, device=dev)
         wts = torch.empty((n, K), dtype=torch.float32, device=dev)
-        kernels.moe_topk(ids, wts, z, self._bias32, E)
+        if self.routing == "sigmoid_groups":
+            kernels.moe_topk_sigmoid(ids, wts, z, self._bias32, E, self.groups, self.group_keep)
+        else:
+            kernels.moe_topk(ids, wts, z, self._bias32, E)
         pairs = n * K
-        up3, down3 = self.up.view(E, F, D), self.down.view(E, D, F)
+        FU = 2 * F if self.gated else F                     # rows of an expert's first matrix
+        act = None if self.gated else self.activation
+        up3, down3 = self.up.view(E, FU, D), self.down.view(E, D, F)
         # bfloat16: the experts' products run on the tensor cores (tiles of 128 rows); float32, or sizes that the
         # 16-byte copies cannot take: the FFMA kernel (tiles of 64 rows)
         use_tc = USE_TC and F % 8 == 0 and kernels.moe_grouped_tc_supported(h, up3) and down3.data_ptr() % 16 == 0
@@ -82,14 +107,20 @@ class RoutedExperts(FeedForward):
         tiles = book[E + 1 + 2 * pairs:E + 1 + 2 * pairs + 4 * max_tiles].view(max_tiles, 4)
         meta = book[E + 1 + 2 * pairs + 4 * max_tiles:]
         kernels.moe_align(ids, E, tile_rows, offsets, pair_row, row_token, tiles, meta)
-        y = torch.empty((pairs, F), dtype=h.dtype, device=dev)
+        y = torch.empty((pairs, FU), dtype=h.dtype, device=dev)
         d = torch.empty((pairs, D), dtype=torch.float32, device=dev)
+        flag = ctx.error_flag if ctx is not None else None
         if use_tc:
-            flag = ctx.error_flag if ctx is not None else None
-            kernels.moe_grouped_tc(y, h, up3, row_token, tiles, meta, act=self.activation, error_flag=flag)
+            kernels.moe_grouped_tc(y, h, up3, row_token, tiles, meta, act=act, error_flag=flag)
+        else:
+            kernels.moe_grouped(y, h, up3, row_token, tiles, meta, act=act)
+        if self.gated:                                      # [pairs, gate | up] -> [pairs, F]
+            y2 = torch.empty((pairs, F), dtype=h.dtype, device=dev)
+            kernels.clamped_glu(y2, y, self.limit, self.alpha)
+            y = y2
+        if use_tc:
             kernels.moe_grouped_tc(d, y, down3, None, tiles, meta, error_flag=flag)
         else:
-            kernels.moe_grouped(y, h, up3, row_token, tiles, meta, act=self.activation)
             kernels.moe_grouped(d, y, down3, None, tiles, meta)
         shared = None
         if self.shared_size:
