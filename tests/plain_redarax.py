@@ -143,7 +143,7 @@ def route(h, W, r):
     sigmoid scores themselves."""
     T = h.shape[0]
     E, top = r["experts"], r["top"]
-    s = sigmoid(h.float() @ W["router"].float().T).to(h.dtype) if h.dtype == torch.float32 else sigmoid(h @ W["router"].T)
+    s = sigmoid(h @ W["router"].T)
     c = s + W["correction"]
     groups = r.get("groups")
     if groups and groups["count"] > 1:
@@ -245,4 +245,35 @@ def tensor_shapes(config):
                 out.update({p + "mlp.router": (E, D), p + "mlp.correction": (E,)})
         if side:
             out.update({p + "side.gate": (side["dim"], D), p + "side.proj": (D, side["dim"]), p + "side.norm": (D,)})
+    return out
+
+
+def random_weights(config, seed=0, dtype=torch.bfloat16, gain=1.0):
+    """Random weights of a size that keeps every branch alive: matrices N(0, gain^2 / fan-in), norm weights near 1, decays
+    and step sizes spread over their useful range, corrections and biases small but not zero."""
+    g = torch.Generator().manual_seed(seed)
+    rnd = lambda *s: torch.randn(*s, generator=g)
+    uni = lambda n, lo, hi: lo + (hi - lo) * torch.rand(n, generator=g)
+    out = {}
+    for name, shape in tensor_shapes(config).items():
+        leaf = name.split(".", 1)[1] if name.startswith("l") and name[1].isdigit() else name
+        if leaf in ("norm1", "norm2", "final.norm", "side.norm", "mix.norm", "mix.q.norm", "mix.k.norm"):
+            t = 1.0 + 0.2 * rnd(*shape)
+        elif leaf == "mix.A_log":
+            t = torch.log(uni(shape[0], 0.3, 4.0))
+        elif leaf == "mix.dt_bias":
+            t = uni(shape[0], -3.0, 0.5)
+        elif leaf == "mix.D":
+            t = 1.0 + 0.3 * rnd(*shape)
+        elif leaf == "mlp.correction":
+            t = 0.2 * rnd(*shape)
+        elif leaf.endswith(".b") and len(shape) == 1:
+            t = 0.2 * rnd(*shape)
+        elif leaf.endswith("conv"):
+            t = 0.6 * rnd(*shape)
+        elif leaf in ("embed", "side.embed"):
+            t = rnd(*shape)
+        else:
+            t = rnd(*shape) * gain / math.sqrt(shape[-1])
+        out[name] = t.to(dtype)
     return out

@@ -1,0 +1,540 @@
+"""The Redarax design in the engine against the plain implementation of tests/plain_redarax.py: every mechanism alone,
+then whole models (tiny, random, sizes that share nothing with each other) through the step function, the trace program
+and the generation entry point."""
+import json
+import math
+import os
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+import plain_redarax as P
+import traces
+import util
+from redarax_configs import BLOCK, CONFIGS
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TDT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+_folders, _oracles = {}, {}
+
+
+def dev(t, dtype=None):
+    return t.to(DEV) if dtype is None else t.to(device=DEV, dtype=dtype)
+
+
+def i32(values):
+    return torch.tensor(values, dtype=torch.int32, device=DEV)
+
+
+def folder_of(name, gain=1.0):
+    """(folder with config.json and model.safetensors in bfloat16, the weights as the plain implementation takes them)."""
+    from lmsf_b200.weights.safetensors_io import write_safetensors
+    key = (name, gain)
+    if key not in _folders:
+        cfg = CONFIGS[name]
+        w = P.random_weights(cfg, seed=sum(map(ord, name)), dtype=torch.bfloat16, gain=gain)
+        d = tempfile.mkdtemp(prefix=f"lmsf_red_{name}_")
+        with open(os.path.join(d, "config.json"), "w") as f:
+            json.dump(cfg, f)
+        write_safetensors(os.path.join(d, "model.safetensors"), [(n, t.dtype, tuple(t.shape)) for n, t in w.items()], lambda n: w[n])
+        _folders[key] = (d, w)
+    return _folders[key]
+
+
+def oracle(name, reqs, gain=1.0):
+    _, w = folder_of(name, gain)
+    out = {}
+    for rid, toks in reqs.items():
+        key = (name, gain, tuple(toks))
+        if key not in _oracles:
+            _oracles[key] = P.forward(CONFIGS[name], w, toks, dtype=torch.float64).float().numpy()
+        out[rid] = _oracles[key]
+    return out
+
+
+def requests_for(name, lengths, seed=0):
+    return {f"q{i}": util.random_ids(n, CONFIGS[name]["vocab"], seed + 11 * i) for i, n in enumerate(lengths)}
+
+
+def worst_rel(rows, ref):
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    return max(float(np.abs(row - ref[rid][pos]).max()) for (rid, pos), row in rows.items()) / scale
+
+
+def position_errors(rows, ref):
+    errs = []
+    for (rid, pos), row in rows.items():
+        d = row - ref[rid][pos]
+        d = d - d.mean()
+        errs.append(float(np.sqrt((d ** 2).mean()) / np.sqrt((ref[rid][pos] ** 2).mean())))
+    return np.sort(np.asarray(errs))
+
+
+F32_TOL = 3e-5
+
+
+def assert_close(rows, ref, dtype, what):
+    """float32: every logit within 3e-5 of the largest.  bfloat16: a token whose rounded router scores choose another expert
+    moves far, in every way of cutting alike, so the bound is on the bulk of the positions; what bfloat16 could hide beyond
+    that is tested on the mechanisms alone with inputs made to show it."""
+    if dtype == "float32":
+        assert worst_rel(rows, ref) <= F32_TOL, (what, worst_rel(rows, ref))
+    else:
+        e = position_errors(rows, ref)
+        assert e[len(e) // 2] <= 3e-2 and e[int(0.9 * len(e))] <= 0.15, (what, e[len(e) // 2], e[int(0.9 * len(e))])
+
+
+# ----------------------------------------------------------------------------- mechanisms alone
+
+def test_a_branch_is_normed_scaled_and_added_and_the_stream_handed_on():
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(0)
+    for n, D, dt in ((5, 72, "float32"), (3, 200, "bfloat16"), (2, 1030, "bfloat16")):
+        res, y, w = torch.randn(n, D, generator=g), torch.randn(n, D, generator=g).to(TDT[dt]), 1 + 0.3 * torch.randn(D, generator=g)
+        want = res.double() + 0.37 * P.rms_norm(y.double(), w.double(), 1e-5)
+        r, h = dev(res), torch.empty((n, D), dtype=TDT[dt], device=DEV)
+        kernels.stream_norm(r, y=dev(y), w_post=dev(w), eps_post=1e-5, h=h, branch_scale=0.37)
+        assert torch.allclose(r.cpu().double(), want, rtol=1e-6, atol=1e-6)
+        assert torch.equal(h.cpu(), r.cpu().to(TDT[dt]))
+        first = torch.empty((n, D), dtype=torch.float32, device=DEV)
+        kernels.stream_begin(first, dev(y))
+        assert torch.equal(first.cpu(), y.float())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,dk,hd,rot,neox", [(4, 2, 24, 32, 10, False), (3, 3, 16, 48, 16, False), (2, 1, 64, 64, 32, True), (5, 1, 8, 16, 0, False)])
+def test_norm_of_queries_and_keys_rotation_and_cache_write_in_one_kernel(dtype, H, G, dk, hd, rot, neox):
+    """Heads wider than the normed size (zero-padded), partial rotation in both pairings, pages out of order."""
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(1)
+    tdt, n, bs = TDT[dtype], 11, 4
+    pos = [0, 1, 2, 3, 4, 5, 6, 40, 41, 1000, 7]
+    seq = [0] * 7 + [1, 1, 2, 0]
+    q, k, v = (torch.zeros(n, heads * hd) for heads in (H, G, G))
+    for t, heads in ((q, H), (k, G)):
+        t.view(n, heads, hd)[:, :, :dk] = torch.randn(n, heads, dk, generator=g)
+    v.copy_(torch.randn(n, G * hd, generator=g))
+    q, k, v = q.to(tdt), k.to(tdt), v.to(tdt)
+    wq, wk = 1 + 0.3 * torch.randn(dk, generator=g), 1 + 0.3 * torch.randn(dk, generator=g)
+    table = torch.full((3, 260), -1, dtype=torch.int32)
+    pages = iter(torch.randperm(40, generator=g).tolist())
+    for s, p in zip(seq, pos):
+        if table[s, p // bs] < 0:
+            table[s, p // bs] = next(pages)
+    cache = torch.zeros((40, 2, G, bs, hd), dtype=tdt, device=DEV)
+    inv = torch.tensor([7000.0 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float32) if rot else None
+    qd = dev(q).clone()
+    kernels.qk_norm_rope_cache_write(qd, dev(k), dev(v), i32(pos), i32(seq), dev(table), bs, cache, dev(inv) if rot else None, rot,
+                                     neox, H, G, hd, dk, dev(wq), dev(wk), 1e-5)
+
+    def want(x, heads, w):
+        x = P.rms_norm(x.double().view(n, heads, hd)[:, :, :dk], w.double(), 1e-5)
+        if rot and not neox:
+            x = P.rotate_interleaved(x, torch.tensor(pos), rot, 7000.0)
+        elif rot:
+            a = torch.tensor(pos, dtype=torch.float64)[:, None] * inv.double()[None, :]
+            c, s = torch.cos(a)[:, None], torch.sin(a)[:, None]
+            u, w2 = x[..., :rot // 2].clone(), x[..., rot // 2:rot].clone()
+            x[..., :rot // 2], x[..., rot // 2:rot] = u * c - w2 * s, w2 * c + u * s
+        return x
+    tol = dict(rtol=1e-5, atol=2e-4) if dtype == "float32" else dict(rtol=1e-2, atol=1e-2)      # float32 angles at position 1,000
+    got_q = qd.cpu().double().view(n, H, hd)
+    assert torch.allclose(got_q[:, :, :dk], want(q, H, wq), **tol) and float(got_q[:, :, dk:].abs().max() if hd > dk else 0) == 0
+    wk_rows = want(k, G, wk)
+    c = cache.cpu().double()
+    for t in range(n):
+        page, slot = int(table[seq[t], pos[t] // bs]), pos[t] % bs
+        assert torch.allclose(c[page, 0, :, slot, :dk], wk_rows[t], **tol)
+        assert torch.equal(c[page, 1, :, slot].reshape(-1), v[t].double())
+    assert int((c.abs().sum(-1) > 0).sum()) <= 2 * G * n            # nothing else was touched
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("C,taps,bias", [(70, 4, True), (5, 2, False), (130, 1, True), (64, 3, False)])
+def test_convolution_carries_its_last_inputs_from_step_to_step(dtype, C, taps, bias):
+    """Portions of one to 300 tokens (longer than a block's chunk), requests side by side, the rest of a slot untouched."""
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(2)
+    tdt = TDT[dtype]
+    lens = [300, 9, 1]
+    xs = [torch.randn(L, C, generator=g).to(tdt) for L in lens]
+    w, b = torch.randn(C, taps, generator=g), torch.randn(C, generator=g) if bias else None
+    want = [P.silu(P.causal_conv(x.double(), w.double(), b.double() if bias else None)) for x in xs]
+    off = 13
+    state = torch.zeros((4, off + (taps - 1) * C + 3), dtype=torch.float32, device=DEV)
+    slots = [2, 0, 3]
+    done, outs = [0, 0, 0], [[], [], []]
+    cuts = [[1, 2, 270, 27], [4, 1, 1, 3], [1]]
+    step = 0
+    while any(d < L for d, L in zip(done, lens)):
+        rows, cu, sl, who = [], [0], [], []
+        for r in range(3):
+            if done[r] < lens[r] and step < len(cuts[r]):
+                m = cuts[r][step]
+                rows.append(xs[r][done[r]:done[r] + m])
+                cu.append(cu[-1] + m)
+                sl.append(slots[r])
+                who.append((r, m))
+        x = dev(torch.cat(rows))
+        wide = torch.zeros((x.shape[0], C + 6), dtype=tdt, device=DEV)       # a view with a row stride of its own
+        wide[:, 3:3 + C] = x
+        out = torch.empty((x.shape[0], C), dtype=tdt, device=DEV)
+        kernels.causal_conv(out, wide[:, 3:3 + C], dev(w), dev(b) if bias else None, state, off, i32(cu), i32(sl), len(sl),
+                            max(m for _, m in who), act="silu")
+        for j, (r, m) in enumerate(who):
+            outs[r].append(out[cu[j]:cu[j + 1]].cpu())
+            done[r] += m
+        step += 1
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == "float32" else dict(rtol=2e-2, atol=2e-2)
+    for r in range(3):
+        assert torch.allclose(torch.cat(outs[r]).double(), want[r], **tol), r
+    st = state.cpu()
+    assert float(st[:, :off].abs().max()) == 0 and float(st[:, off + (taps - 1) * C:].abs().max()) == 0 and float(st[1].abs().max()) == 0
+
+
+def plain_scan(q, k, v, dt_raw, beta_raw, dt_bias, a_log, skip, H, G, delta, unit, S=None):
+    """Token by token in float64; q, k: [T, G, dk], v: [T, H, dv].  Returns (outputs [T, H, dv], states [H, dk, dv])."""
+    T, dk, dv = q.shape[0], q.shape[2], v.shape[2]
+    S = torch.zeros(H, dk, dv, dtype=torch.float64) if S is None else S.clone()
+    out = torch.zeros(T, H, dv, dtype=torch.float64)
+    if unit:
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    dt = P.softplus(dt_raw + dt_bias)
+    a = torch.exp(-torch.exp(a_log) * dt)
+    for t in range(T):
+        for h in range(H):
+            gq = h // (H // G)
+            if delta:
+                S[h] = a[t, h] * S[h]
+                u = P.sigmoid(beta_raw[t, h]) * (v[t, h] - S[h].T @ k[t, gq])
+                S[h] = S[h] + torch.outer(k[t, gq], u)
+            else:
+                S[h] = a[t, h] * S[h] + dt[t, h] * torch.outer(k[t, gq], v[t, h])
+            out[t, h] = S[h].T @ q[t, gq] + (skip[h] * v[t, h] if skip is not None else 0)
+    return out, S
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("delta", [False, True])
+@pytest.mark.parametrize("H,G,dk,dv", [(4, 2, 12, 20), (1, 1, 7, 5), (2, 1, 130, 33), (6, 6, 64, 40), (3, 1, 17, 64)])
+def test_scan_in_portions_and_token_by_token(dtype, delta, H, G, dk, dv):
+    """Two requests of unequal length in one launch; the whole against portions of 1 to 19 tokens, which must agree bit
+    for bit (the state is carried exactly); slots that held rubbish and were zeroed; the plain rule and the delta rule."""
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(3)
+    tdt = TDT[dtype]
+    lens = [45, 18]
+    data = []
+    for L in lens:
+        data.append(dict(q=torch.randn(L, G * dk, generator=g).to(tdt), k=torch.randn(L, G * dk, generator=g).to(tdt),
+                         v=torch.randn(L, H * dv, generator=g).to(tdt), dt=torch.randn(L, H, generator=g).to(tdt),
+                         beta=torch.randn(L, H, generator=g).to(tdt)))
+    dt_bias, a_log = -2 + 2 * torch.rand(H, generator=g), torch.log(0.3 + 3 * torch.rand(H, generator=g))
+    skip = None if delta else 1 + 0.3 * torch.randn(H, generator=g)
+    extra = 9                                                 # what follows the matrices in a slot must stay untouched
+    size = H * dk * dv + extra
+
+    def run(cuts):
+        state = torch.full((5, size), 7.0, dtype=torch.float32, device=DEV)
+        slots = [3, 1]
+        for s in slots:
+            state[s].zero_()
+        done, outs = [0, 0], [[], []]
+        for step in range(max(len(c) for c in cuts)):
+            who = [(r, cuts[r][step]) for r in range(2) if step < len(cuts[r])]
+            cu = [0]
+            for _, m in who:
+                cu.append(cu[-1] + m)
+            cat = {key: dev(torch.cat([data[r][key][done[r]:done[r] + m] for r, m in who])) for key in ("q", "k", "v", "dt", "beta")}
+            out = torch.empty((cu[-1], H * dv), dtype=torch.float32, device=DEV)
+            kernels.gated_scan(out, cat["q"], cat["k"], cat["v"], cat["dt"], cat["beta"] if delta else None, dev(dt_bias), dev(a_log),
+                               dev(skip) if skip is not None else None, state, i32(cu), i32([slots[r] for r, _ in who]), len(who),
+                               H, G, dk, dv, delta=delta, k_times_dt=not delta, unit_qk=delta, q_scale=dk ** -0.5 if delta else 1.0)
+            for j, (r, m) in enumerate(who):
+                outs[r].append(out[cu[j]:cu[j + 1]].cpu())
+                done[r] += m
+        assert done == lens
+        return [torch.cat(o) for o in outs], state.cpu()
+    whole, st_whole = run([[45], [18]])
+    parts, st_parts = run([[1, 19, 2, 16, 7], [5, 1, 1, 11]])
+    ones, st_ones = run([[1] * 45, [1] * 18])
+    for r in range(2):
+        assert torch.equal(whole[r], parts[r]) and torch.equal(whole[r], ones[r])
+    assert torch.equal(st_whole, st_parts) and torch.equal(st_whole, st_ones)
+    assert float((st_whole[[0, 2, 4]] - 7).abs().max()) == 0 and float(st_whole[:, H * dk * dv:][[1, 3]].abs().max()) == 0
+    for r, L in enumerate(lens):
+        d = {key: t.double() for key, t in data[r].items()}
+        want, S = plain_scan(d["q"].view(L, G, dk), d["k"].view(L, G, dk), d["v"].view(L, H, dv), d["dt"], d["beta"], dt_bias.double(),
+                             a_log.double(), skip.double() if skip is not None else None, H, G, delta, delta)
+        scale = float(want.abs().max())
+        assert float((whole[r].double().view(L, H, dv) - want).abs().max()) <= 2e-5 * scale
+        got_S = st_whole[[3, 1][r], :H * dk * dv].double().view(H, dv, dk).transpose(1, 2)
+        assert float((got_S - S).abs().max()) <= 2e-5 * max(1.0, float(S.abs().max()))
+
+
+def test_the_delta_rule_recalls_a_value_written_long_ago():
+    """One key far back is orthogonal to all later keys: with a decay of almost one it is still read exactly 400 tokens
+    later, and not at all when the reading query misses it by a dimension."""
+    from lmsf_b200 import kernels
+    H, dk, dv, T = 1, 8, 4, 402
+    k = torch.zeros(T, dk)
+    k[0, 0] = 1.0
+    k[1:, 1] = 1.0                                # later keys all alike: they overwrite each other, not the first
+    v = torch.randn(T, dv, generator=torch.Generator().manual_seed(4))
+    q = torch.zeros(T, dk)
+    q[-2, 0] = 1.0                                # reads the first write
+    q[-1, 2] = 1.0                                # reads nothing
+    dt = torch.full((T, 1), -30.0)                # softplus ~ 1e-13: no decay to speak of
+    beta = torch.full((T, 1), 30.0)               # sigmoid ~ 1
+    state = torch.zeros((1, dk * dv), dtype=torch.float32, device=DEV)
+    out = torch.empty((T, dv), dtype=torch.float32, device=DEV)
+    kernels.gated_scan(out, dev(q), dev(k), dev(v), dev(dt), dev(beta), dev(torch.zeros(1)), dev(torch.zeros(1)), None, state,
+                       i32([0, T]), i32([0]), 1, H, 1, dk, dv, delta=True, unit_qk=True, q_scale=1.0)
+    o = out.cpu()
+    assert torch.allclose(o[-2], v[0], rtol=1e-5, atol=1e-5) and float(o[-1].abs().max()) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_over_groups_with_the_gate_before_or_after(dtype):
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(5)
+    tdt = TDT[dtype]
+    for n, groups, size, wlen, first in ((7, 3, 24, 72, True), (4, 1, 1500, 1500, True), (5, 6, 40, 40, False), (3, 2, 8, 8, False)):
+        x, z, w = torch.randn(n, groups * size, generator=g), torch.randn(n, groups * size, generator=g).to(tdt), 1 + 0.3 * torch.randn(wlen, generator=g)
+        xd, zd = x.double().view(n, groups, size), z.double().view(n, groups, size)
+        wd = w.double().view(groups, size) if wlen == groups * size else w.double()
+        want = P.rms_norm(xd * P.silu(zd), None, 1e-5) * wd if first else P.rms_norm(xd, None, 1e-5) * wd * P.silu(zd)
+        out = torch.empty((n, groups * size), dtype=tdt, device=DEV)
+        kernels.grouped_gated_norm(out, dev(x), dev(z), dev(w), size, 1e-5, gate_act="silu", gate_first=first)
+        tol = dict(rtol=1e-5, atol=1e-5) if dtype == "float32" else dict(rtol=1e-2, atol=1e-2)
+        assert torch.allclose(out.cpu().double().view(n, groups, size), want, **tol)
+
+
+def test_router_chooses_inside_the_best_groups_and_weighs_by_the_scores():
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(6)
+    for n, E, top, count, keep in ((200, 8, 2, 2, 1), (64, 6, 2, 3, 2), (50, 12, 3, 4, 2), (33, 5, 2, 5, 3), (20, 4, 4, 2, 2), (40, 7, 3, 1, 1), (9, 1, 1, 1, 1)):
+        z, corr = 2 * torch.randn(n, E + 2, generator=g), torch.randn(E, generator=g) - 1.5       # most choice scores negative
+        ids = torch.empty((n, top), dtype=torch.int32, device=DEV)
+        wts = torch.empty((n, top), dtype=torch.float32, device=DEV)
+        kernels.moe_topk_sigmoid(ids, wts, dev(z), dev(corr), E, count, keep)
+        W = {"router": torch.eye(E, dtype=torch.float64), "correction": corr.double()}
+        want_ids, want_w = P.route(z[:, :E].double(), W, {"experts": E, "top": top, "groups": {"count": count, "keep": keep}})
+        assert torch.equal(ids.cpu().long().sort(-1).values, want_ids.sort(-1).values), (E, top, count, keep)
+        order = ids.cpu().long().argsort(-1), want_ids.argsort(-1)
+        assert torch.allclose(wts.cpu().double().gather(1, order[0]), want_w.gather(1, order[1]), rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_small_kernels_of_the_feed_forward_the_side_branch_and_the_head(dtype):
+    from lmsf_b200 import kernels
+    g = torch.Generator().manual_seed(7)
+    tdt = TDT[dtype]
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == "float32" else dict(rtol=1e-2, atol=1e-2)
+    x = (3 * torch.randn(9, 2 * 37, generator=g)).to(tdt)
+    out = torch.empty((9, 37), dtype=tdt, device=DEV)
+    kernels.clamped_glu(out, dev(x), 1.3)
+    gd, ud = torch.clamp(x.double()[:, :37], max=1.3), torch.clamp(x.double()[:, 37:], -1.3, 1.3)
+    assert torch.allclose(out.cpu().double(), gd * P.sigmoid(1.702 * gd) * (ud + 1), **tol)
+    a, table, ids = torch.randn(6, 5, generator=g).to(tdt), torch.randn(11, 20, generator=g).to(tdt), [3, 10, 0, 3, 7, 1]
+    out = torch.empty((6, 5), dtype=tdt, device=DEV)
+    kernels.gelu_mul_gather(out, dev(a), dev(table), 10, i32(ids))
+    assert torch.allclose(out.cpu().double(), P.gelu_tanh(a.double()) * table.double()[ids][:, 10:15], **tol)
+    y = 20 * torch.randn(4, 33, generator=g)
+    yd = dev(y).clone()
+    kernels.scale_softcap_(yd, 1.7, 9.0)
+    assert torch.allclose(yd.cpu().double(), 9.0 * torch.tanh(y.double() * 1.7 / 9.0), rtol=1e-5, atol=1e-5)
+    yd = dev(y).clone()
+    kernels.scale_softcap_(yd, 0.5, 0.0)
+    assert torch.allclose(yd.cpu(), y * 0.5)
+
+
+def _context(seqs, block_size, n_pages, seed, dtype):
+    """A StepContext built by hand for requests (tokens so far, tokens now); pages dealt out of order, the same pages
+    for the same seed."""
+    from lmsf_b200.parts.base import CacheGroupView, StepContext
+    g = torch.Generator().manual_seed(seed)
+    perm = iter(torch.randperm(n_pages, generator=g).tolist())
+    max_blocks = max((a + b + block_size - 1) // block_size for a, b in seqs)
+    table = torch.full((len(seqs), max_blocks), -1, dtype=torch.int32)
+    pos, seq, cu, ctxl = [], [], [0], []
+    for s, (a, b) in enumerate(seqs):
+        for j in range((a + b + block_size - 1) // block_size):
+            table[s, j] = next(perm)
+        pos += list(range(a, a + b))
+        seq += [s] * b
+        cu.append(cu[-1] + b)
+        ctxl.append(a + b)
+    n = len(pos)
+    dec = [i for i, (_, b) in enumerate(seqs) if b == 1]
+    tiles = lambda size: [(i, q0) for i, (_, b) in enumerate(seqs) if b > 1 for q0 in range(0, b, size)]
+    t64, t128 = tiles(64), tiles(128)
+    return StepContext(n_tokens=n, n_seqs=len(seqs), dtype=dtype, device=torch.device(DEV), token_ids=i32([0] * n),
+                       positions=i32(pos), token_seq=i32(seq), cu_q=i32(cu), ctx_len=i32(ctxl), state_slot=i32(list(range(len(seqs)))),
+                       groups=[CacheGroupView(dev(table), block_size)], q_lens=[b for _, b in seqs], ctx_lens=ctxl,
+                       state_slots=list(range(len(seqs))), error_flag=torch.zeros(1, dtype=torch.int32, device=DEV),
+                       decode_seq_ids=i32(dec or [0]), n_decode_seqs=len(dec),
+                       q_tile_seq=i32([t[0] for t in t64] or [0]), q_tile_q0=i32([t[1] for t in t64] or [0]), n_q_tiles=len(t64),
+                       q_tile128_seq=i32([t[0] for t in t128] or [0]), q_tile128_q0=i32([t[1] for t in t128] or [0]), n_q_tiles128=len(t128))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far", [0, 15, 16, 17, 255, 256, 380])
+def test_attention_finds_a_key_far_back_at_and_around_page_borders(dtype, far):
+    """Queries and keys share their weights and the norm's weight is large, so that a token whose input equals the last
+    token's is the one key that the last query sees (apart from itself); the values differ by the token alone (the
+    value projection reads a column that only this test sets).  The far token sits at the sequence's first place, at
+    the last slot of a page, at the first of the next, and hundreds of tokens back; the prompt is run whole and with
+    its last token decoded alone."""
+    from lmsf_b200.parts.attention import PagedAttention
+    from lmsf_b200.parts.base import LayerCache
+    from lmsf_b200.parts.rope import RotaryEmbedding
+    g = torch.Generator().manual_seed(8)
+    tdt = TDT[dtype]
+    D, H, G, dk, dv, T, bs = 48, 4, 2, 24, 40, 400, 16
+    m = {"heads": H, "kv_heads": G, "dim": dk, "vdim": dv, "scale": 1.0, "rot": {"dims": 4, "base": 1.0e6}}
+    Wq = torch.randn(H * dk, D, generator=g) / math.sqrt(D)
+    Wq[:, D - 1] = 0                              # the last column of the input tags the token: values see it, q and k do not
+    qk_w = torch.full((dk,), 1.5)
+    qk_w[:4] = 0.05                               # the rotated dimensions weigh little: a match survives any distance
+    W = {"q": Wq, "k": Wq.view(G, H // G, dk, D)[:, 0].reshape(G * dk, D).clone(), "v": torch.randn(G * dv, D, generator=g) / math.sqrt(D),
+         "q.b": torch.zeros(H * dk), "k.b": torch.zeros(G * dk), "v.b": 0.1 * torch.randn(G * dv, generator=g),
+         "q.norm": qk_w, "k.norm": qk_w.clone(), "o": torch.randn(D, H * dv, generator=g) / math.sqrt(H * dv),
+         "o.b": 0.1 * torch.randn(D, generator=g)}
+    W = {n: t.to(torch.bfloat16).float() for n, t in W.items()}
+    h = torch.randn(T, D, generator=g)
+    h[far, :D - 1] = h[T - 1, :D - 1]
+    h[:, D - 1] *= 3
+    h = h.to(tdt)
+    want = P.attention_mixer(h.double(), {n: t.double() for n, t in W.items()}, m, 1e-5)[T - 1]
+    missed = h.clone()
+    missed[far, :D - 1] = -missed[far, :D - 1]
+    miss = P.attention_mixer(missed.double(), {n: t.double() for n, t in W.items()}, m, 1e-5)[T - 1]
+    assert float((want - miss).abs().max()) > 0.1 * float(want.abs().max())          # the far key matters
+    part = PagedAttention(D, H, G, dk, position_encoding=RotaryEmbedding(4, 1.0e6, is_neox=False), scale=1.0, bias=True,
+                          value_dim=dv, qk_norm=True, qk_norm_eps=1e-5)
+    part.set_weights({"qkv": dev(torch.cat([W["q"], W["k"], W["v"]]), tdt), "qkv_bias": dev(torch.cat([W["q.b"], W["k.b"], W["v.b"]]), tdt),
+                      "o": dev(W["o"], tdt), "o_bias": dev(W["o.b"], tdt), "q_norm": dev(W["q.norm"], tdt), "k_norm": dev(W["k.norm"], tdt)})
+    part.prepare(tdt, torch.device(DEV))
+    for cuts in ([T], [T - 1, 1], [far + 1, T - far - 2, 1] if 0 < far < T - 3 else [3, T - 4, 1]):
+        cache = LayerCache(kv=torch.zeros((40, 2, G, bs, part.head_dim), dtype=tdt, device=DEV), group=0)
+        done = 0
+        for c in cuts:
+            ctx = _context([(done, c)], bs, 40, 9, tdt)
+            out = part.forward(ctx, dev(h[done:done + c]), cache)
+            assert int(ctx.error_flag.item()) == 0
+            done += c
+        got = out[-1].cpu().double()
+        tol = 2e-5 if dtype == "float32" else 3e-2
+        assert float((got - want).abs().max()) <= tol * float(want.abs().max()), (cuts, float((got - want).abs().max()))
+
+
+# ----------------------------------------------------------------------------- whole models through the step function
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["X", "Y", "Z"])
+def test_every_way_of_cutting_agrees_with_the_plain_implementation(name, dtype):
+    """Whole prompts, prefill then token by token, portions of several sizes down to two tokens, and batches of unequal
+    requests with few pages and three state slots (pages and slots are used again)."""
+    folder, _ = folder_of(name)
+    reqs = requests_for(name, [61, 5, 1, 130, 33, 18, 290 if name == "X" else 77])
+    ref = oracle(name, reqs)
+    bs = BLOCK[name]
+    modes = {"whole": traces.whole(reqs), "decode": traces.whole(reqs, tail=30), "portions": traces.portions(reqs, [2, 7, 3, 16, 2, 29]),
+             "pairs": traces.portions(reqs, [2]), "mixed": traces.mixed(reqs, seed=4, max_live=3, tail=10)}
+    got = {}
+    for mode, steps in modes.items():
+        out = traces.run_inprocess(folder, dtype, steps, bs, traces.max_live_tokens(steps, 64), max_live=3)
+        got[mode] = traces.collect(steps, out)
+        assert len(got[mode]) == sum(len(t) for t in reqs.values())
+        assert_close(got[mode], ref, dtype, mode)
+    if dtype == "float32":                            # a position's logits do not depend on the cut beyond rounding
+        for mode in modes:
+            for key, row in got[mode].items():
+                assert np.abs(row - got["whole"][key]).max() <= 2e-5 * np.abs(got["whole"][key]).max(), (mode, key)
+
+
+def test_long_decoding_replays_graphs_and_equals_eager_steps():
+    """A short prompt, then 150 single tokens over several pages; the decode steps are replayed from a CUDA graph, and
+    must equal the eager steps."""
+    from lmsf_b200.engine.factory import build_model
+    from lmsf_b200.engine.model_runner import ModelRunner, StepEntry
+    folder, _ = folder_of("X")
+    reqs = requests_for("X", [160, 158], seed=3)
+    ref = oracle("X", reqs)
+    model, _, tdt = build_model(folder, "float32", DEV)
+    assert all(getattr(p, "graph_safe", False) for p, _ in model.parts_with_specs())
+    rows = {}
+    for eager in (False, True):
+        runner = ModelRunner(model, tdt, torch.device(DEV), 8, num_blocks=48, max_num_seqs=3, enforce_eager=eager)
+        mgr = runner.make_cache_manager()
+        for rid in reqs:
+            mgr.add(rid)
+        runner.step([StepEntry(rid, reqs[rid][:8], []) for rid in reqs], mgr)
+        got = {rid: [] for rid in reqs}
+        for t in range(8, 158):
+            lg = runner.step([StepEntry(rid, [reqs[rid][t]], [0]) for rid in reqs], mgr)
+            for j, rid in enumerate(reqs):
+                got[rid].append(lg[j].cpu().numpy())
+        assert (len(runner._graphs) > 0) == (not eager)
+        rows[eager] = got
+        for rid in reqs:
+            mgr.free(rid)
+    for rid in reqs:
+        scale = float(np.abs(ref[rid]).max())
+        for i, (a, b) in enumerate(zip(rows[False][rid], rows[True][rid])):
+            assert np.abs(a - ref[rid][8 + i]).max() <= F32_TOL * scale, (rid, i)
+            assert np.abs(a - b).max() <= 1e-5 * scale
+
+
+def test_a_freed_state_slot_starts_from_zero():
+    """One state slot: a second request gets the slot of the first, whose state and carried inputs must not leak into it."""
+    folder, _ = folder_of("Y")
+    reqs = requests_for("Y", [40, 40], seed=9)
+    ref = oracle("Y", reqs)
+    steps = traces.portions(reqs, [13, 2])
+    out = traces.run_inprocess(folder, "float32", steps, 16, 64, max_live=1)
+    assert worst_rel(traces.collect(steps, out), ref) <= F32_TOL
+
+
+def test_larger_weights_keep_the_comparison_sharp():
+    """With three times the weights the attention, the router and the clamps are far from their linear range."""
+    folder, _ = folder_of("Z", gain=3.0)
+    reqs = requests_for("Z", [90, 17], seed=5)
+    ref = oracle("Z", reqs, gain=3.0)
+    steps = traces.mixed(reqs, seed=1, max_live=2, tail=6)
+    out = traces.run_inprocess(folder, "float32", steps, 16, traces.max_live_tokens(steps, 64), max_live=2)
+    assert worst_rel(traces.collect(steps, out), ref) <= 6e-5
+
+
+def test_the_trace_program_runs_the_design():
+    folder, _ = folder_of("Y")
+    reqs = requests_for("Y", [30, 9], seed=2)
+    ref = oracle("Y", reqs)
+    steps = traces.mixed(reqs, seed=3, max_live=2, tail=4)
+    out = traces.run_program(folder, "float32", steps, traces.max_live_tokens(steps, 64))
+    assert worst_rel(traces.collect(steps, out), ref) <= F32_TOL
+
+
+def test_greedy_generation_through_the_engine():
+    """The generation entry point with its scheduler, continuous batching and sampler: greedy tokens in float32 equal
+    those of the plain implementation fed its own tokens back."""
+    from lmsf_b200 import LLM, SamplingParams
+    folder, w = folder_of("X")
+    cfg = CONFIGS["X"]
+    prompts = [util.random_ids(n, cfg["vocab"], 50 + i) for i, n in enumerate([23, 4, 41])]
+    llm = LLM(folder, dtype="float32", block_size=8, num_gpu_blocks=48, max_num_batched_tokens=24, max_num_seqs=3)
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        toks = list(p)
+        for _ in range(12):
+            lg = P.forward(cfg, w, toks, dtype=torch.float64)[-1]
+            nxt = int(lg.argmax())
+            got = o.outputs[0].token_ids[len(toks) - len(p)]
+            if got != nxt:                             # only a near tie may be decided otherwise
+                assert float(lg[nxt] - lg[got]) <= 1e-4 * float(lg.abs().max())
+            toks.append(got)
