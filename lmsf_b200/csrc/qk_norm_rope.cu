@@ -97,6 +97,85 @@ __global__ void __launch_bounds__(kWarps * 32) qk_norm_rope_kernel(QkNormRopeArg
   }
 }
 
+// Interleaved pairs (or no rotation) and a head of 32 * VW values: a lane holds VW consecutive values of the head in
+// registers from the load to the store, so a pair never leaves its lane and nothing passes through shared memory but
+// the token's cosines and sines.  Needs rows and heads aligned to VW values.
+template <typename T, int VW> struct alignas(sizeof(T) * VW) HeadVec { T v[VW]; };
+
+template <typename T, int VW>
+__global__ void __launch_bounds__(kWarps * 32) qk_norm_rope_vec_kernel(QkNormRopeArgs a) {
+  extern __shared__ float smem[];                 // cos[half], sin[half]
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pos = a.positions[t];
+  const int half = a.inv_freq ? a.rot_dim / 2 : 0;
+  float* cs = smem;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float s, c;
+    sincosf((float)pos * a.inv_freq[i], &s, &c);
+    cs[i] = c;
+    cs[half + i] = s;
+  }
+  __syncthreads();
+  const int hd = a.head_dim;
+  T* kc = nullptr;
+  T* vc = nullptr;
+  if (a.cache) {
+    const int page = a.block_table[(size_t)a.token_seq[t] * a.max_blocks + pos / a.block_size];
+    if (page < 0) {
+      if (threadIdx.x == 0 && a.error_flag) atomicExch(a.error_flag, 2);
+    } else {
+      kc = (T*)a.cache + (size_t)page * a.page_stride + (size_t)(pos % a.block_size) * hd;
+      vc = kc + (size_t)a.n_kv_heads * a.block_size * hd;
+    }
+  }
+  const size_t head_pitch = (size_t)a.block_size * hd;
+  const int n_k = a.cache ? a.n_kv_heads : 0;
+  const int e0 = lane * VW;
+  typedef HeadVec<T, VW> Vec;
+  for (int head = warp + kWarps * blockIdx.y; head < a.n_q_heads + 2 * n_k; head += kWarps * gridDim.y) {
+    if (head >= a.n_q_heads + n_k) {
+      const int g = head - a.n_q_heads - n_k;
+      if (vc) *reinterpret_cast<Vec*>(vc + g * head_pitch + e0) =
+          *reinterpret_cast<const Vec*>((const T*)a.v + (size_t)t * a.v_stride + (size_t)g * hd + e0);
+      continue;
+    }
+    const bool is_q = head < a.n_q_heads;
+    const int g = is_q ? head : head - a.n_q_heads;
+    if (!is_q && !kc) continue;
+    const T* src = is_q ? (const T*)a.q + (size_t)t * a.q_stride + (size_t)g * hd
+                        : (const T*)a.k + (size_t)t * a.k_stride + (size_t)g * hd;
+    T* dst = is_q ? (T*)a.q + (size_t)t * a.q_stride + (size_t)g * hd : kc + g * head_pitch;
+    const float* w = is_q ? a.wq : a.wk;
+    Vec raw = *reinterpret_cast<const Vec*>(src + e0);
+    float x[VW];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VW; ++j) {
+      x[j] = to_f32(raw.v[j]);
+      if (e0 + j < a.norm_dim) ss = fmaf(x[j], x[j], ss);
+    }
+    ss = warp_sum(ss);
+    if (w) {
+      const float inv = 1.0f / sqrtf(ss / (float)a.norm_dim + a.eps);
+#pragma unroll
+      for (int j = 0; j < VW; ++j)
+        if (e0 + j < a.norm_dim) x[j] = (x[j] * inv) * w[e0 + j];
+    }
+#pragma unroll
+    for (int j = 0; j < VW; j += 2) {
+      if (e0 + j < 2 * half) {
+        const int p = (e0 + j) >> 1;
+        const float c = cs[p], s = cs[half + p], u = x[j], v = x[j + 1];
+        x[j] = rot_first(u, v, c, s);
+        x[j + 1] = rot_second(u, v, c, s);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < VW; ++j) raw.v[j] = from_f32<T>(x[j]);
+    *reinterpret_cast<Vec*>(dst + e0) = raw;
+  }
+}
+
 }  // namespace lmsf
 
 // q: [n, n_q_heads * head_dim] (changed in place), k, v: [n, n_kv_heads * head_dim], rows of `dtype` with the given strides;
@@ -122,6 +201,22 @@ LMSF_API int lmsf_qk_norm_rope_cache_write(void* q, const void* k, const void* v
   const size_t smem = ((inv_freq ? rot_dim : 0) + (size_t)kWarps * head_dim) * sizeof(float);
   if (smem > 48 * 1024) LMSF_REFUSE("qk_norm_rope: head_dim=%d is too wide", head_dim);
   cudaStream_t s = (cudaStream_t)stream;
+  if (dtype != LMSF_F32 && dtype != LMSF_BF16) LMSF_REFUSE("qk_norm_rope: unknown dtype code %d", dtype);
+  const int vw = head_dim / 32;
+  const size_t esz = dtype == LMSF_F32 ? 4 : 2;
+  if ((!inv_freq || !is_neox) && head_dim % 32 == 0 && (vw == 2 || vw == 4 || vw == 8) && q_stride % vw == 0 &&
+      (!cache || (k_stride % vw == 0 && v_stride % vw == 0 && page_stride % vw == 0)) &&
+      ((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)cache) % (esz * vw) == 0) {
+    const int heads = n_q_heads + (cache ? 2 * n_kv_heads : 0);
+    // few tokens (a decode step): a token's heads are spread over several blocks
+    dim3 grid(n_tokens, n_tokens >= 256 ? 1 : (heads >= 32 ? 4 : (heads >= 8 ? 2 : 1)));
+    const size_t cs_bytes = (inv_freq ? rot_dim : 0) * sizeof(float);
+#define LMSF_GO(T, VW) qk_norm_rope_vec_kernel<T, VW><<<grid, kWarps * 32, cs_bytes, s>>>(a)
+    if (dtype == LMSF_F32) { if (vw == 2) LMSF_GO(float, 2); else if (vw == 4) LMSF_GO(float, 4); else LMSF_GO(float, 8); }
+    else { if (vw == 2) LMSF_GO(bf16, 2); else if (vw == 4) LMSF_GO(bf16, 4); else LMSF_GO(bf16, 8); }
+#undef LMSF_GO
+    return LMSF_LAUNCH_STATUS();
+  }
   if (dtype == LMSF_F32) qk_norm_rope_kernel<float><<<n_tokens, kWarps * 32, smem, s>>>(a);
   else if (dtype == LMSF_BF16) qk_norm_rope_kernel<bf16><<<n_tokens, kWarps * 32, smem, s>>>(a);
   else LMSF_REFUSE("qk_norm_rope: unknown dtype code %d", dtype);

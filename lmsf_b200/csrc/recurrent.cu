@@ -77,6 +77,114 @@ __global__ void causal_conv_kernel(T* __restrict__ out, long long out_stride, co
   }
 }
 
+// The same with VEC channels per thread (one 16-byte access of the activation type) and a window that slides in
+// registers: a thread owns its channels for a chunk of kConvVecChunk tokens, reads every input once (and taps - 1 rows
+// before the chunk), and, in a request's first chunk, is also the only reader and writer of its channels' state.
+constexpr int kConvVecChunk = 16;
+constexpr int kConvVecThreads = 128;
+
+template <typename T, int VEC> __device__ __forceinline__ void conv_load(const T* p, float (&v)[VEC]);
+template <> __device__ __forceinline__ void conv_load<float, 4>(const float* p, float (&v)[4]) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+template <> __device__ __forceinline__ void conv_load<bf16, 8>(const bf16* p, float (&v)[8]) {
+  const uint4 x = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+}
+template <typename T, int VEC> __device__ __forceinline__ void conv_store(T* p, const float (&v)[VEC]);
+template <> __device__ __forceinline__ void conv_store<float, 4>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void conv_store<bf16, 8>(bf16* p, const float (&v)[8]) {
+  uint4 x;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+  *reinterpret_cast<uint4*>(p) = x;
+}
+
+template <typename T, int VEC, int TAPS>
+__global__ void __launch_bounds__(kConvVecThreads) causal_conv_vec_kernel(
+    T* __restrict__ out, long long out_stride, const T* __restrict__ x, long long x_stride, const float* __restrict__ w,
+    const float* __restrict__ bias, float* __restrict__ state, long long slot_stride, const int* __restrict__ cu_q,
+    const int* __restrict__ state_slot, int C, int act) {
+  const int c = (blockIdx.x * kConvVecThreads + threadIdx.x) * VEC;
+  const int s = blockIdx.y;
+  const int t0 = cu_q[s], n = cu_q[s + 1] - t0;
+  const int lo = blockIdx.z * kConvVecChunk;
+  if (lo >= n || c >= C) return;
+  const int hi = min(n, lo + kConvVecChunk);
+  float* st = state + (size_t)state_slot[s] * slot_stride;      // [TAPS - 1][C]
+  float wr[TAPS][VEC], b[VEC], win[TAPS > 1 ? TAPS - 1 : 1][VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    b[e] = bias ? bias[c + e] : 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) wr[j][e] = w[(size_t)(c + e) * TAPS + j];
+  }
+  // the TAPS - 1 inputs before the chunk, oldest first: from the portion, or (before its first token) from the state
+#pragma unroll
+  for (int j = 0; j < TAPS - 1; ++j) {
+    const int u = lo - (TAPS - 1) + j;
+    if (u >= 0) conv_load<T, VEC>(x + (size_t)(t0 + u) * x_stride + c, win[j]);
+    else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) win[j][e] = st[(size_t)(TAPS - 1 + u) * C + c + e];
+    }
+  }
+  for (int t = lo; t < hi; ++t) {
+    float cur[VEC], acc[VEC];
+    conv_load<T, VEC>(x + (size_t)(t0 + t) * x_stride + c, cur);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      float a = b[e];
+#pragma unroll
+      for (int j = 0; j < TAPS - 1; ++j) a = fmaf(wr[j][e], win[j][e], a);
+      a = fmaf(wr[TAPS - 1][e], cur[e], a);
+      acc[e] = act ? silu_f(a) : a;
+    }
+    conv_store<T, VEC>(out + (size_t)(t0 + t) * out_stride + c, acc);
+#pragma unroll
+    for (int j = 0; j + 1 < TAPS - 1; ++j)
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) win[j][e] = win[j + 1][e];
+    if (TAPS > 1) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) win[TAPS - 2][e] = cur[e];
+    }
+  }
+  if (blockIdx.z != 0 || TAPS == 1) return;
+  // the request's first chunk also rolls the state on (this thread alone reads and writes these channels of it)
+  if (n <= kConvVecChunk) {                        // the window now holds the last TAPS - 1 inputs
+#pragma unroll
+    for (int j = 0; j < TAPS - 1; ++j)
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) st[(size_t)j * C + c + e] = win[j][e];
+  } else {                                         // they lie at the end of the portion (n > TAPS - 1)
+#pragma unroll
+    for (int j = 0; j < TAPS - 1; ++j) {
+      float v[VEC];
+      conv_load<T, VEC>(x + (size_t)(t0 + n - (TAPS - 1) + j) * x_stride + c, v);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) st[(size_t)j * C + c + e] = v[e];
+    }
+  }
+}
+
+template <typename T, int VEC>
+static int launch_conv_vec(void* out, long long out_stride, const void* x, long long x_stride, const float* w, const float* bias,
+                           float* state, long long slot_stride, const int* cu_q, const int* state_slot, int n_seqs, int max_q, int C,
+                           int taps, int act, cudaStream_t s) {
+  dim3 grid(ceil_div(C, VEC * kConvVecThreads), n_seqs, ceil_div(max_q, kConvVecChunk));
+#define LMSF_CASE(TP) case TP: causal_conv_vec_kernel<T, VEC, TP><<<grid, kConvVecThreads, 0, s>>>((T*)out, out_stride, (const T*)x, x_stride, w, bias, state, slot_stride, cu_q, state_slot, C, act); break;
+  switch (taps) { LMSF_CASE(1) LMSF_CASE(2) LMSF_CASE(3) LMSF_CASE(4) LMSF_CASE(5) LMSF_CASE(6) LMSF_CASE(7) LMSF_CASE(8) default: return LMSF_EBADARG; }
+#undef LMSF_CASE
+  return LMSF_LAUNCH_STATUS();
+}
+
 // ---------------------------------------------------------------------------------------------- scan
 
 struct ScanArgs {
@@ -93,17 +201,22 @@ struct ScanArgs {
   float unit_eps, q_scale;
 };
 
-constexpr int kScanTokens = 16;     // tokens staged in shared memory at a time
 constexpr int kScanCols = 32;       // columns of the state per block
 
 // grid (column tiles, heads, requests); 256 threads: thread = (column c = tid / 8, row lane r = tid % 8), rows r + 8 m.
+// A chunk of tokens is staged in shared memory (q and k scaled, the token's decay and write strength computed once);
+// a row of q or k lies there so that the values m = 4 j .. 4 j + 3 of lane r are one 16-byte word at (j * 8 + r) * 4: the
+// eight lanes of a column read consecutive words.  Sums over the rows run in four chains that are added at the end
+// (a fixed order).
 template <typename T, int ROWS, bool DELTA>
 __global__ void __launch_bounds__(256) gated_scan_kernel(ScanArgs a) {
-  constexpr int DKP = 8 * ROWS;
-  __shared__ float sq[kScanTokens][DKP];
-  __shared__ float sk[kScanTokens][DKP];
-  __shared__ float sv[kScanTokens][kScanCols];
-  __shared__ float sa[kScanTokens], sb[kScanTokens];
+  constexpr int RV = (ROWS + 3) / 4;              // 16-byte words per lane and row
+  constexpr int RL = RV * 32;                     // floats of a staged row
+  constexpr int CH = ROWS <= 16 ? 32 : 16;        // tokens staged at a time
+  __shared__ __align__(16) float sq[CH][RL];
+  __shared__ __align__(16) float sk[CH][RL];
+  __shared__ float sv[CH][kScanCols];
+  __shared__ float sa[CH], sb[CH];
   const int tid = threadIdx.x, c = tid >> 3, r = tid & 7, lane = tid & 31, warp = tid >> 5;
   const int head = blockIdx.y, seq = blockIdx.z, col = blockIdx.x * kScanCols + c;
   const int g = head / (a.H / a.G);
@@ -119,8 +232,8 @@ __global__ void __launch_bounds__(256) gated_scan_kernel(ScanArgs a) {
   }
   const float bias = a.dt_bias[head], rate = expf(a.a_log[head]);
   const float skip = a.skip ? a.skip[head] : 0.f;
-  for (int base = 0; base < n; base += kScanTokens) {
-    const int cnt = min(kScanTokens, n - base);
+  for (int base = 0; base < n; base += CH) {
+    const int cnt = min(CH, n - base);
     __syncthreads();
     for (int tt = warp; tt < cnt; tt += 8) {
       const size_t t = (size_t)(t0 + base + tt);
@@ -141,9 +254,10 @@ __global__ void __launch_bounds__(256) gated_scan_kernel(ScanArgs a) {
       }
       const float dt = softplus_f(to_f32(((const T*)a.dt)[t * a.dt_stride + head]) + bias);
       if (a.k_times_dt) fk *= dt;
-      for (int i = lane; i < DKP; i += 32) {
-        sq[tt][i] = i < a.dk ? to_f32(qp[i]) * fq : 0.f;
-        sk[tt][i] = i < a.dk ? to_f32(kp[i]) * fk : 0.f;
+      for (int i = lane; i < 8 * RV * 4; i += 32) {              // row i = r + 8 m lies at ((m / 4) * 8 + r) * 4 + m % 4
+        const int rr = i & 7, m = i >> 3, at = ((m >> 2) * 8 + rr) * 4 + (m & 3);
+        sq[tt][at] = i < a.dk ? to_f32(qp[i]) * fq : 0.f;
+        sk[tt][at] = i < a.dk ? to_f32(kp[i]) * fk : 0.f;
       }
       if (lane == 0) {
         sa[tt] = expf(-rate * dt);
@@ -155,30 +269,39 @@ __global__ void __launch_bounds__(256) gated_scan_kernel(ScanArgs a) {
     __syncthreads();
     for (int tt = 0; tt < cnt; ++tt) {
       const float dec = sa[tt], vv = sv[tt][c];
+      float kk[RV * 4], qq[RV * 4];
+#pragma unroll
+      for (int j = 0; j < RV; ++j) {
+        const float4 x = *reinterpret_cast<const float4*>(&sk[tt][(j * 8 + r) * 4]);
+        const float4 y = *reinterpret_cast<const float4*>(&sq[tt][(j * 8 + r) * 4]);
+        kk[4 * j] = x.x; kk[4 * j + 1] = x.y; kk[4 * j + 2] = x.z; kk[4 * j + 3] = x.w;
+        qq[4 * j] = y.x; qq[4 * j + 1] = y.y; qq[4 * j + 2] = y.z; qq[4 * j + 3] = y.w;
+      }
+      float u = vv;
       if (DELTA) {
-        float p = 0.f;
+        float p[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int m = 0; m < ROWS; ++m) {
           S[m] *= dec;
-          p = fmaf(S[m], sk[tt][r + 8 * m], p);
+          p[m & 3] = fmaf(S[m], kk[m], p[m & 3]);
         }
-        p += __shfl_xor_sync(0xffffffffu, p, 4);
-        p += __shfl_xor_sync(0xffffffffu, p, 2);
-        p += __shfl_xor_sync(0xffffffffu, p, 1);
-        const float u = sb[tt] * (vv - p);
-#pragma unroll
-        for (int m = 0; m < ROWS; ++m) S[m] = fmaf(sk[tt][r + 8 * m], u, S[m]);
-      } else {
-#pragma unroll
-        for (int m = 0; m < ROWS; ++m) S[m] = fmaf(sk[tt][r + 8 * m], vv, dec * S[m]);
+        float ps = (p[0] + p[1]) + (p[2] + p[3]);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 4);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        u = sb[tt] * (vv - ps);
       }
-      float o = 0.f;
+      float o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int m = 0; m < ROWS; ++m) o = fmaf(S[m], sq[tt][r + 8 * m], o);
-      o += __shfl_xor_sync(0xffffffffu, o, 4);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      if (r == 0 && live) a.out[(size_t)(t0 + base + tt) * a.out_stride + (size_t)head * a.dv + col] = fmaf(skip, vv, o);
+      for (int m = 0; m < ROWS; ++m) {
+        S[m] = DELTA ? fmaf(kk[m], u, S[m]) : fmaf(kk[m], u, dec * S[m]);
+        o[m & 3] = fmaf(S[m], qq[m], o[m & 3]);
+      }
+      float os = (o[0] + o[1]) + (o[2] + o[3]);
+      os += __shfl_xor_sync(0xffffffffu, os, 4);
+      os += __shfl_xor_sync(0xffffffffu, os, 2);
+      os += __shfl_xor_sync(0xffffffffu, os, 1);
+      if (r == 0 && live) a.out[(size_t)(t0 + base + tt) * a.out_stride + (size_t)head * a.dv + col] = fmaf(skip, vv, os);
     }
   }
   if (live) {
@@ -235,6 +358,45 @@ __global__ void grouped_gated_norm_kernel(T* __restrict__ out, long long out_str
   }
 }
 
+// The same with a group's values held in registers between the sum of squares and the scaling (PER per member of the
+// team): x and the gate are read once.
+template <typename T, bool BLOCK, int PER>
+__global__ void __launch_bounds__(BLOCK ? 256 : 128) grouped_gated_norm_reg_kernel(
+    T* __restrict__ out, long long out_stride, const float* __restrict__ x, long long x_stride, const T* __restrict__ gate,
+    long long gate_stride, const float* __restrict__ w, int wlen, int n, int n_groups, int gsize, float eps, int gate_silu,
+    int gate_first) {
+  __shared__ float scratch[33];
+  const int team = BLOCK ? blockIdx.x : blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int me = BLOCK ? threadIdx.x : (threadIdx.x & 31), step = BLOCK ? 256 : 32;
+  if (team >= n * n_groups) return;
+  const int t = team / n_groups, grp = team % n_groups;
+  const float* xr = x + (size_t)t * x_stride + (size_t)grp * gsize;
+  const T* gr = gate ? gate + (size_t)t * gate_stride + (size_t)grp * gsize : nullptr;
+  float v[PER], gv[PER];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = me + step * j;
+    v[j] = i < gsize ? xr[i] : 0.f;
+    gv[j] = 1.f;
+    if (gr && i < gsize) { const float z = to_f32(gr[i]); gv[j] = gate_silu ? silu_f(z) : sigmoid_f(z); }
+    if (gate_first) v[j] *= gv[j];
+    ss = fmaf(v[j], v[j], ss);
+  }
+  ss = BLOCK ? block_sum(ss, scratch) : warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)gsize + eps);
+  T* o = out + (size_t)t * out_stride + (size_t)grp * gsize;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = me + step * j;
+    if (i < gsize) {
+      float r = (v[j] * inv) * w[(grp * gsize + i) % wlen];
+      if (!gate_first) r *= gv[j];
+      o[i] = from_f32<T>(r);
+    }
+  }
+}
+
 }  // namespace lmsf
 
 // x: [n, C] rows of `dtype` with x_stride elements between tokens; out likewise; w: float32 [C, taps]; bias: float32 [C] or
@@ -247,9 +409,17 @@ LMSF_API int lmsf_causal_conv(void* out, long long out_stride, const void* x, lo
   if (n_seqs <= 0 || max_q <= 0) return 0;
   if (C <= 0 || taps < 1 || taps > kMaxTaps) LMSF_REFUSE("causal_conv: %d channels, %d taps (1 to %d taps)", C, taps, kMaxTaps);
   if (n_seqs > 65535) LMSF_REFUSE("causal_conv: more than 65535 requests in one launch");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (ceil_div(max_q, kConvVecChunk) > 65535) LMSF_REFUSE("causal_conv: a portion of %d tokens is too long for one launch", max_q);
+  // 16-byte accesses where the rows allow them (the state's rows are then 16-byte aligned too)
+  const int vec = dtype == LMSF_F32 ? 4 : 8;
+  if ((dtype == LMSF_F32 || dtype == LMSF_BF16) && C % vec == 0 && out_stride % vec == 0 && x_stride % vec == 0 &&
+      ((uintptr_t)out | (uintptr_t)x) % 16 == 0) {
+    if (dtype == LMSF_F32) return launch_conv_vec<float, 4>(out, out_stride, x, x_stride, w, bias, state, slot_stride, cu_q, state_slot, n_seqs, max_q, C, taps, act, s);
+    return launch_conv_vec<bf16, 8>(out, out_stride, x, x_stride, w, bias, state, slot_stride, cu_q, state_slot, n_seqs, max_q, C, taps, act, s);
+  }
   dim3 grid(ceil_div(C, kConvChannels), n_seqs, ceil_div(max_q, kConvChunk));
   dim3 block(kConvChannels, max_q >= 4 ? 4 : (max_q >= 2 ? 2 : 1));
-  cudaStream_t s = (cudaStream_t)stream;
   if (dtype == LMSF_F32)
     causal_conv_kernel<float><<<grid, block, 0, s>>>((float*)out, out_stride, (const float*)x, x_stride, w, bias, state, slot_stride, cu_q, state_slot, C, taps, act);
   else if (dtype == LMSF_BF16)
@@ -290,6 +460,24 @@ LMSF_API int lmsf_grouped_gated_norm(void* out, long long out_stride, const floa
   const long long teams = (long long)n * n_groups;
   const bool block = gsize > 1024;
   const unsigned blocks = (unsigned)(block ? teams : (teams + 3) / 4);
+  const int per = ceil_div(gsize, block ? 256 : 32);
+#define LMSF_REG(T, B, P) grouped_gated_norm_reg_kernel<T, B, P><<<blocks, B ? 256 : 128, 0, s>>>((T*)out, out_stride, x, x_stride, (const T*)gate, gate_stride, w, wlen, n, n_groups, gsize, eps, gate_silu, gate_first)
+#define LMSF_PICK(T)                                                                         \
+  if (!block) {                                                                              \
+    if (per <= 2) { LMSF_REG(T, false, 2); return LMSF_LAUNCH_STATUS(); }                     \
+    if (per <= 4) { LMSF_REG(T, false, 4); return LMSF_LAUNCH_STATUS(); }                     \
+    if (per <= 8) { LMSF_REG(T, false, 8); return LMSF_LAUNCH_STATUS(); }                     \
+    if (per <= 16) { LMSF_REG(T, false, 16); return LMSF_LAUNCH_STATUS(); }                   \
+    LMSF_REG(T, false, 32); return LMSF_LAUNCH_STATUS();                                      \
+  } else if (per <= 32) {                                                                    \
+    if (per <= 8) { LMSF_REG(T, true, 8); return LMSF_LAUNCH_STATUS(); }                      \
+    if (per <= 16) { LMSF_REG(T, true, 16); return LMSF_LAUNCH_STATUS(); }                    \
+    LMSF_REG(T, true, 32); return LMSF_LAUNCH_STATUS();                                       \
+  }
+  if (dtype == LMSF_F32) { LMSF_PICK(float) }
+  else if (dtype == LMSF_BF16) { LMSF_PICK(bf16) }
+#undef LMSF_PICK
+#undef LMSF_REG
 #define LMSF_GO(T, B) grouped_gated_norm_kernel<T, B><<<blocks, B ? 256 : 128, 0, s>>>((T*)out, out_stride, x, x_stride, (const T*)gate, gate_stride, w, wlen, n, n_groups, gsize, eps, gate_silu, gate_first)
   if (dtype == LMSF_F32) { if (block) LMSF_GO(float, true); else LMSF_GO(float, false); }
   else if (dtype == LMSF_BF16) { if (block) LMSF_GO(bf16, true); else LMSF_GO(bf16, false); }
