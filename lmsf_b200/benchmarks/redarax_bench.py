@@ -110,10 +110,10 @@ def kernels_alone(pk, width=4096, heads=32, dim=128, experts=64, top=6):
         bias, alog, skip = rnd(Hs, dtype=f32), rnd(Hs, dtype=f32), (None if delta else ones(Hs))
         kw = dict(delta=delta, k_times_dt=not delta, unit_qk=delta, q_scale=dk ** -0.5 if delta else 1.0)
         per_token = (6.0 if delta else 4.0) * Hs * dk * dv
-        rec(f"{name}: one prompt of 2048 tokens as one chain",
+        rec(f"{name}: one prompt of 2048 tokens as one chain (prepare + scan)",
             tm.run(lambda: kernels.gated_scan(o, qs, ks, vs, dt, beta if delta else None, bias, alog, skip, state, cu1, sl1, 1, Hs, Gs, dk, dv, **kw), 1, 3),
             flops=per_token * T, like="lightning_scan as one chain below")
-        rec(f"{name}: decode of 64 requests (reads and writes 64 x {Hs * dk * dv * 4 // 1024} KB of state)",
+        rec(f"{name}: decode of 64 requests (reads and writes 64 x {Hs * dk * dv * 4 // 1024} KB of state; prepare + scan)",
             tm.run(lambda: kernels.gated_scan(o[:64], qs[:64], ks[:64], vs[:64], dt[:64], beta[:64] if delta else None, bias, alog, skip, state,
                                               cu64, sl64, 64, Hs, Gs, dk, dv, **kw), 3, 10),
             bytes_=64 * Hs * dk * dv * 4 * 2, like="lightning_scan decode below")

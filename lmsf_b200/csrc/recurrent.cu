@@ -16,6 +16,8 @@
 //                 taken over each group of `gsize` columns, the weight indexed by column modulo its length
 //
 // The state of a head is stored transposed, [dv][dk]: the eight threads that share a column read consecutive rows.
+// The scan is two launches: scan_prepare (per token: q and k scaled into the scan's layout, decay, write strength, step
+// size) and the scan itself, whose blocks stage chunks of tokens by plain copies.
 #include "common.cuh"
 
 LMSF_DEFINE_LAST_ERROR(lmsf_recurrent)
@@ -80,7 +82,7 @@ __global__ void causal_conv_kernel(T* __restrict__ out, long long out_stride, co
 // The same with VEC channels per thread (one 16-byte access of the activation type) and a window that slides in
 // registers: a thread owns its channels for a chunk of kConvVecChunk tokens, reads every input once (and taps - 1 rows
 // before the chunk), and, in a request's first chunk, is also the only reader and writer of its channels' state.
-constexpr int kConvVecChunk = 16;
+constexpr int kConvVecChunk = 8;
 constexpr int kConvVecThreads = 128;
 
 template <typename T, int VEC> __device__ __forceinline__ void conv_load(const T* p, float (&v)[VEC]);
@@ -135,6 +137,7 @@ __global__ void __launch_bounds__(kConvVecThreads) causal_conv_vec_kernel(
       for (int e = 0; e < VEC; ++e) win[j][e] = st[(size_t)(TAPS - 1 + u) * C + c + e];
     }
   }
+#pragma unroll 4
   for (int t = lo; t < hi; ++t) {
     float cur[VEC], acc[VEC];
     conv_load<T, VEC>(x + (size_t)(t0 + t) * x_stride + c, cur);
@@ -199,26 +202,73 @@ struct ScanArgs {
   int H, G, dk, dv;
   int k_times_dt, unit_qk;
   float unit_eps, q_scale;
+  float* qf; float* kf; float4* gates;                         // what scan_prepare leaves for the scan (below)
+  int n_tokens;
 };
 
 constexpr int kScanCols = 32;       // columns of the state per block
+constexpr int kScanLanes = 8;       // threads that share a column: thread = (column c = tid / 8, row lane r = tid % 8)
 
-// grid (column tiles, heads, requests); 256 threads: thread = (column c = tid / 8, row lane r = tid % 8), rows r + 8 m.
-// A chunk of tokens is staged in shared memory (q and k scaled, the token's decay and write strength computed once);
-// a row of q or k lies there so that the values m = 4 j .. 4 j + 3 of lane r are one 16-byte word at (j * 8 + r) * 4: the
-// eight lanes of a column read consecutive words.  Sums over the rows run in four chains that are added at the end
-// (a fixed order).
+// Row i = r + 8 m of a q or k vector lies at ((m / 4) * 8 + r) * 4 + m % 4 of its staged row of `rl` floats: the values
+// m = 4 j .. 4 j + 3 of lane r are one 16-byte word, and the eight lanes of a column read consecutive words.
+__device__ __forceinline__ int scan_place(int i) {
+  const int r = i & 7, m = i >> 3;
+  return ((m >> 2) * 8 + r) * 4 + (m & 3);
+}
+
+// Before the scan, once per token: q and k of every q/k head as float32 in the scan's own layout (made unit vectors and
+// scaled, if asked; zero beyond dk), and per head the token's decay, write strength and step size.  A warp per (token,
+// q/k head); the scan then stages its chunks by plain 16-byte copies that do not wait on each other.
+template <typename T>
+__global__ void __launch_bounds__(128) scan_prepare_kernel(ScanArgs a, int rl) {
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int g = warp; g < a.G; g += 4) {
+    const T* qp = (const T*)a.q + (size_t)t * a.q_stride + (size_t)g * a.dk;
+    const T* kp = (const T*)a.k + (size_t)t * a.k_stride + (size_t)g * a.dk;
+    float fq = 1.f, fk = 1.f;
+    if (a.unit_qk) {
+      float ssq = 0.f, ssk = 0.f;
+      for (int i = lane; i < a.dk; i += 32) {
+        const float x = to_f32(qp[i]), y = to_f32(kp[i]);
+        ssq = fmaf(x, x, ssq);
+        ssk = fmaf(y, y, ssk);
+      }
+      ssq = warp_sum(ssq);
+      ssk = warp_sum(ssk);
+      fq = a.q_scale / sqrtf(ssq + a.unit_eps);
+      fk = 1.0f / sqrtf(ssk + a.unit_eps);
+    }
+    float* qo = a.qf + ((size_t)t * a.G + g) * rl;
+    float* ko = a.kf + ((size_t)t * a.G + g) * rl;
+    for (int i = lane; i < rl; i += 32) {
+      const int at = scan_place(i);
+      qo[at] = i < a.dk ? to_f32(qp[i]) * fq : 0.f;
+      ko[at] = i < a.dk ? to_f32(kp[i]) * fk : 0.f;
+    }
+  }
+  for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
+    const float dt = softplus_f(to_f32(((const T*)a.dt)[(size_t)t * a.dt_stride + h]) + a.dt_bias[h]);
+    const float dec = expf(-expf(a.a_log[h]) * dt);
+    const float beta = a.beta ? sigmoid_f(to_f32(((const T*)a.beta)[(size_t)t * a.beta_stride + h])) : 1.f;
+    a.gates[(size_t)t * a.H + h] = make_float4(dec, beta, a.k_times_dt ? dt : 1.f, 0.f);
+  }
+}
+
+// grid (column tiles, heads, requests); 256 threads; rows r + 8 m of a column in registers.  A chunk of tokens is staged
+// in shared memory; sums over the rows run in four chains that are added at the end, then over the eight lanes by a
+// butterfly (a fixed order).
 template <typename T, int ROWS, bool DELTA>
 __global__ void __launch_bounds__(256) gated_scan_kernel(ScanArgs a) {
+  constexpr int R = kScanLanes, COLS = kScanCols;
   constexpr int RV = (ROWS + 3) / 4;              // 16-byte words per lane and row
-  constexpr int RL = RV * 32;                     // floats of a staged row
-  constexpr int CH = ROWS <= 16 ? 32 : 16;        // tokens staged at a time
+  constexpr int RL = RV * 4 * R;                  // floats of a staged row
+  constexpr int CH = RL <= 128 ? 32 : 16;         // tokens staged at a time
   __shared__ __align__(16) float sq[CH][RL];
   __shared__ __align__(16) float sk[CH][RL];
-  __shared__ float sv[CH][kScanCols];
-  __shared__ float sa[CH], sb[CH];
-  const int tid = threadIdx.x, c = tid >> 3, r = tid & 7, lane = tid & 31, warp = tid >> 5;
-  const int head = blockIdx.y, seq = blockIdx.z, col = blockIdx.x * kScanCols + c;
+  __shared__ float sv[CH][COLS];
+  __shared__ float4 sg[CH];
+  const int tid = threadIdx.x, c = tid / R, r = tid % R;
+  const int head = blockIdx.y, seq = blockIdx.z, col = blockIdx.x * COLS + c;
   const int g = head / (a.H / a.G);
   const int t0 = a.cu_q[seq], n = a.cu_q[seq + 1] - t0;
   if (n <= 0) return;
@@ -227,57 +277,37 @@ __global__ void __launch_bounds__(256) gated_scan_kernel(ScanArgs a) {
   float S[ROWS];
 #pragma unroll
   for (int m = 0; m < ROWS; ++m) {
-    const int i = r + 8 * m;
+    const int i = r + R * m;
     S[m] = (live && i < a.dk) ? st[(size_t)col * a.dk + i] : 0.f;
   }
-  const float bias = a.dt_bias[head], rate = expf(a.a_log[head]);
   const float skip = a.skip ? a.skip[head] : 0.f;
   for (int base = 0; base < n; base += CH) {
     const int cnt = min(CH, n - base);
     __syncthreads();
-    for (int tt = warp; tt < cnt; tt += 8) {
-      const size_t t = (size_t)(t0 + base + tt);
-      const T* qp = (const T*)a.q + t * a.q_stride + (size_t)g * a.dk;
-      const T* kp = (const T*)a.k + t * a.k_stride + (size_t)g * a.dk;
-      float fq = 1.f, fk = 1.f;
-      if (a.unit_qk) {
-        float ssq = 0.f, ssk = 0.f;
-        for (int i = lane; i < a.dk; i += 32) {
-          const float x = to_f32(qp[i]), y = to_f32(kp[i]);
-          ssq = fmaf(x, x, ssq);
-          ssk = fmaf(y, y, ssk);
-        }
-        ssq = warp_sum(ssq);
-        ssk = warp_sum(ssk);
-        fq = a.q_scale / sqrtf(ssq + a.unit_eps);
-        fk = 1.0f / sqrtf(ssk + a.unit_eps);
-      }
-      const float dt = softplus_f(to_f32(((const T*)a.dt)[t * a.dt_stride + head]) + bias);
-      if (a.k_times_dt) fk *= dt;
-      for (int i = lane; i < 8 * RV * 4; i += 32) {              // row i = r + 8 m lies at ((m / 4) * 8 + r) * 4 + m % 4
-        const int rr = i & 7, m = i >> 3, at = ((m >> 2) * 8 + rr) * 4 + (m & 3);
-        sq[tt][at] = i < a.dk ? to_f32(qp[i]) * fq : 0.f;
-        sk[tt][at] = i < a.dk ? to_f32(kp[i]) * fk : 0.f;
-      }
-      if (lane == 0) {
-        sa[tt] = expf(-rate * dt);
-        sb[tt] = a.beta ? sigmoid_f(to_f32(((const T*)a.beta)[t * a.beta_stride + head])) : 1.f;
-      }
-      const int cc = blockIdx.x * kScanCols + lane;
-      sv[tt][lane] = cc < a.dv ? to_f32(((const T*)a.v)[t * a.v_stride + (size_t)head * a.dv + cc]) : 0.f;
+    for (int idx = tid; idx < cnt * (RL / 4); idx += 256) {
+      const int tt = idx / (RL / 4), w4 = idx % (RL / 4);
+      const size_t row = ((size_t)(t0 + base + tt) * a.G + g) * RL;
+      *reinterpret_cast<float4*>(&sq[tt][4 * w4]) = *reinterpret_cast<const float4*>(a.qf + row + 4 * w4);
+      *reinterpret_cast<float4*>(&sk[tt][4 * w4]) = *reinterpret_cast<const float4*>(a.kf + row + 4 * w4);
     }
+    for (int idx = tid; idx < cnt * COLS; idx += 256) {
+      const int tt = idx / COLS, cc = blockIdx.x * COLS + idx % COLS;
+      sv[tt][idx % COLS] = cc < a.dv ? to_f32(((const T*)a.v)[(size_t)(t0 + base + tt) * a.v_stride + (size_t)head * a.dv + cc]) : 0.f;
+    }
+    if (tid < cnt) sg[tid] = a.gates[(size_t)(t0 + base + tid) * a.H + head];
     __syncthreads();
     for (int tt = 0; tt < cnt; ++tt) {
-      const float dec = sa[tt], vv = sv[tt][c];
+      const float4 gt = sg[tt];                   // decay, write strength, step size
+      const float dec = gt.x, vv = sv[tt][c];
       float kk[RV * 4], qq[RV * 4];
 #pragma unroll
       for (int j = 0; j < RV; ++j) {
-        const float4 x = *reinterpret_cast<const float4*>(&sk[tt][(j * 8 + r) * 4]);
-        const float4 y = *reinterpret_cast<const float4*>(&sq[tt][(j * 8 + r) * 4]);
+        const float4 x = *reinterpret_cast<const float4*>(&sk[tt][(j * R + r) * 4]);
+        const float4 y = *reinterpret_cast<const float4*>(&sq[tt][(j * R + r) * 4]);
         kk[4 * j] = x.x; kk[4 * j + 1] = x.y; kk[4 * j + 2] = x.z; kk[4 * j + 3] = x.w;
         qq[4 * j] = y.x; qq[4 * j + 1] = y.y; qq[4 * j + 2] = y.z; qq[4 * j + 3] = y.w;
       }
-      float u = vv;
+      float u = gt.z * vv;                        // the plain rule writes (dt k) v^T = k (dt v)^T
       if (DELTA) {
         float p[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -286,10 +316,9 @@ __global__ void __launch_bounds__(256) gated_scan_kernel(ScanArgs a) {
           p[m & 3] = fmaf(S[m], kk[m], p[m & 3]);
         }
         float ps = (p[0] + p[1]) + (p[2] + p[3]);
-        ps += __shfl_xor_sync(0xffffffffu, ps, 4);
-        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
-        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
-        u = sb[tt] * (vv - ps);
+#pragma unroll
+        for (int off = R / 2; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+        u = gt.y * (vv - ps);
       }
       float o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -298,29 +327,38 @@ __global__ void __launch_bounds__(256) gated_scan_kernel(ScanArgs a) {
         o[m & 3] = fmaf(S[m], qq[m], o[m & 3]);
       }
       float os = (o[0] + o[1]) + (o[2] + o[3]);
-      os += __shfl_xor_sync(0xffffffffu, os, 4);
-      os += __shfl_xor_sync(0xffffffffu, os, 2);
-      os += __shfl_xor_sync(0xffffffffu, os, 1);
+#pragma unroll
+      for (int off = R / 2; off > 0; off >>= 1) os += __shfl_xor_sync(0xffffffffu, os, off);
       if (r == 0 && live) a.out[(size_t)(t0 + base + tt) * a.out_stride + (size_t)head * a.dv + col] = fmaf(skip, vv, os);
     }
   }
   if (live) {
 #pragma unroll
     for (int m = 0; m < ROWS; ++m) {
-      const int i = r + 8 * m;
+      const int i = r + R * m;
       if (i < a.dk) st[(size_t)col * a.dk + i] = S[m];
     }
   }
 }
 
+static int scan_rows(int dk) {                     // rows per lane, as the kernel is built: 2, 4, 8, 16 or 32
+  const int rows = ceil_div(dk, kScanLanes);
+  return rows <= 2 ? 2 : rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
+}
+static int scan_row_floats(int dk) { return (scan_rows(dk) + 3) / 4 * 4 * kScanLanes; }
+
 template <typename T, bool DELTA>
 static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t s) {
+  scan_prepare_kernel<T><<<a.n_tokens, 128, 0, s>>>(a, scan_row_floats(a.dk));
   dim3 grid(ceil_div(a.dv, kScanCols), a.H, n_seqs);
-  const int rows = ceil_div(a.dk, 8);
-#define LMSF_CASE(R) if (rows <= R) { gated_scan_kernel<T, R, DELTA><<<grid, 256, 0, s>>>(a); return LMSF_LAUNCH_STATUS(); }
-  LMSF_CASE(2) LMSF_CASE(4) LMSF_CASE(8) LMSF_CASE(16) LMSF_CASE(32)
-#undef LMSF_CASE
-  return LMSF_EBADARG;
+  switch (scan_rows(a.dk)) {
+    case 2: gated_scan_kernel<T, 2, DELTA><<<grid, 256, 0, s>>>(a); break;
+    case 4: gated_scan_kernel<T, 4, DELTA><<<grid, 256, 0, s>>>(a); break;
+    case 8: gated_scan_kernel<T, 8, DELTA><<<grid, 256, 0, s>>>(a); break;
+    case 16: gated_scan_kernel<T, 16, DELTA><<<grid, 256, 0, s>>>(a); break;
+    default: gated_scan_kernel<T, 32, DELTA><<<grid, 256, 0, s>>>(a); break;
+  }
+  return LMSF_LAUNCH_STATUS();
 }
 
 // ---------------------------------------------------------------------------------------------- norm over groups
@@ -428,19 +466,28 @@ LMSF_API int lmsf_causal_conv(void* out, long long out_stride, const void* x, lo
   return LMSF_LAUNCH_STATUS();
 }
 
+// Floats of the scratch that lmsf_gated_scan needs for n_tokens tokens (q and k in the scan's layout, and four floats per
+// token and head).
+LMSF_API long long lmsf_gated_scan_scratch_floats(int n_tokens, int H, int G, int dk) {
+  return (long long)n_tokens * (2LL * G * lmsf::scan_row_floats(dk) + 4LL * H);
+}
+
 LMSF_API int lmsf_gated_scan(float* out, long long out_stride, const void* q, const void* k, const void* v, long long q_stride,
                              long long k_stride, long long v_stride, const void* dt, long long dt_stride, const void* beta,
                              long long beta_stride, const float* dt_bias, const float* a_log, const float* skip, float* state,
-                             long long slot_stride, const int* cu_q, const int* state_slot, int n_seqs, int H, int G, int dk,
-                             int dv, int delta, int k_times_dt, int unit_qk, float unit_eps, float q_scale, int dtype,
-                             void* stream) {
+                             long long slot_stride, const int* cu_q, const int* state_slot, int n_seqs, int n_tokens, int H,
+                             int G, int dk, int dv, int delta, int k_times_dt, int unit_qk, float unit_eps, float q_scale,
+                             float* scratch, int dtype, void* stream) {
   using namespace lmsf;
-  if (n_seqs <= 0) return 0;
+  if (n_seqs <= 0 || n_tokens <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || dk <= 0 || dk > 256 || dv <= 0 || H > 65535 || n_seqs > 65535)
     LMSF_REFUSE("gated_scan: %d heads over %d q/k heads, dk=%d (up to 256), dv=%d", H, G, dk, dv);
   if (delta && !beta) LMSF_REFUSE("gated_scan: the delta rule needs a write strength per head and token");
+  if (!scratch || (uintptr_t)scratch % 16) LMSF_REFUSE("gated_scan: a 16-byte aligned scratch is needed");
+  const long long rowf = (long long)n_tokens * G * scan_row_floats(dk);
   ScanArgs a{out, out_stride, q, k, v, q_stride, k_stride, v_stride, dt, dt_stride, beta, beta_stride, dt_bias, a_log, skip,
-             state, slot_stride, cu_q, state_slot, H, G, dk, dv, k_times_dt, unit_qk, unit_eps, q_scale};
+             state, slot_stride, cu_q, state_slot, H, G, dk, dv, k_times_dt, unit_qk, unit_eps, q_scale,
+             scratch, scratch + rowf, reinterpret_cast<float4*>(scratch + 2 * rowf), n_tokens};
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
   if (dtype == LMSF_F32) rc = delta ? launch_scan<float, true>(a, n_seqs, s) : launch_scan<float, false>(a, n_seqs, s);

@@ -952,7 +952,8 @@ def gated_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Ten
     S += k u^T; out[t, h] = S^T q + skip[h] v.  Head h reads q/k head h // (heads / qk_heads); unit_qk makes q and k unit
     vectors first (x / sqrt(sum x^2 + unit_eps)) and multiplies q by q_scale.  S = the first heads * dv * dk values of
     state[slot] (float32 [slots, size], stored [head][dv][dk]), read before and written after.
-    q, k: [n, qk_heads * dk]; v: [n, heads * dv]; dt, beta: [n, heads] (views of one dtype); out: float32 [n, heads * dv]."""
+    q, k: [n, qk_heads * dk]; v: [n, heads * dv]; dt, beta: [n, heads] (views of one dtype); out: float32 [n, heads * dv].
+    Two launches: one prepares q, k and the tokens' decays in a scratch that this function allocates, one scans."""
     n = q.shape[0]
     _rows(q, qk_heads * dk, "gated_scan: q")
     _rows(k, qk_heads * dk, "gated_scan: k", q.dtype)
@@ -966,13 +967,17 @@ def gated_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Ten
     f = _func("recurrent.cu", "lmsf_gated_scan",
               [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_longlong,
                c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int,
-               c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p])
+    need = _func("recurrent.cu", "lmsf_gated_scan_scratch_floats", [c_int, c_int, c_int, c_int])
+    need.restype = c_longlong
+    scratch = torch.empty(int(need(n, heads, qk_heads, dk)), dtype=torch.float32, device=q.device)
     rc = f(_ptr(out), out.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(dt), dt.stride(0),
            _ptr(beta), beta.stride(0) if beta is not None else 0, _f32vec(dt_bias, heads, "dt_bias"),
            _f32vec(a_log, heads, "a_log"), _f32vec(skip, heads, "skip"), _ptr(state), state.stride(0), _i32(cu_q, "cu_q"),
-           _i32(state_slot, "state_slot"), n_seqs, heads, qk_heads, dk, dv, int(delta), int(k_times_dt), int(unit_qk),
-           float(unit_eps), float(q_scale), dtype_code(q.dtype), _stream())
+           _i32(state_slot, "state_slot"), n_seqs, n, heads, qk_heads, dk, dv, int(delta), int(k_times_dt), int(unit_qk),
+           float(unit_eps), float(q_scale), _ptr(scratch), dtype_code(q.dtype), _stream())
     _check(rc, "recurrent.cu", "lmsf_recurrent")
+    add_launches(1)                                            # two launches: prepare and scan
 
 
 def grouped_gated_norm(out: torch.Tensor, x: torch.Tensor, gate: Optional[torch.Tensor], w: torch.Tensor, group_size: int,

@@ -223,7 +223,7 @@ def plain_scan(q, k, v, dt_raw, beta_raw, dt_bias, a_log, skip, H, G, delta, uni
 @pytest.mark.parametrize("H,G,dk,dv", [(4, 2, 12, 20), (1, 1, 7, 5), (2, 1, 130, 33), (6, 6, 64, 40), (3, 1, 17, 64)])
 def test_scan_in_portions_and_token_by_token(dtype, delta, H, G, dk, dv):
     """Two requests of unequal length in one launch; the whole against portions of 1 to 19 tokens, which must agree bit
-    for bit (the state is carried exactly); slots that held rubbish and were zeroed; the plain rule and the delta rule."""
+    for bit (the state is carried exactly); slots beside rubbish that must stay; the plain rule and the delta rule."""
     from lmsf_b200 import kernels
     g = torch.Generator().manual_seed(3)
     tdt = TDT[dtype]
