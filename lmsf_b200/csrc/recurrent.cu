@@ -82,7 +82,7 @@ __global__ void causal_conv_kernel(T* __restrict__ out, long long out_stride, co
 // The same with VEC channels per thread (one 16-byte access of the activation type) and a window that slides in
 // registers: a thread owns its channels for a chunk of kConvVecChunk tokens, reads every input once (and taps - 1 rows
 // before the chunk), and, in a request's first chunk, is also the only reader and writer of its channels' state.
-constexpr int kConvVecChunk = 8;
+constexpr int kConvVecChunk = 32;
 constexpr int kConvVecThreads = 128;
 
 template <typename T, int VEC> __device__ __forceinline__ void conv_load(const T* p, float (&v)[VEC]);
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(kConvVecThreads) causal_conv_vec_kernel(
       for (int e = 0; e < VEC; ++e) win[j][e] = st[(size_t)(TAPS - 1 + u) * C + c + e];
     }
   }
-#pragma unroll 4
+#pragma unroll 8
   for (int t = lo; t < hi; ++t) {
     float cur[VEC], acc[VEC];
     conv_load<T, VEC>(x + (size_t)(t0 + t) * x_stride + c, cur);
@@ -396,9 +396,12 @@ __global__ void grouped_gated_norm_kernel(T* __restrict__ out, long long out_str
   }
 }
 
-// The same with a group's values held in registers between the sum of squares and the scaling (PER per member of the
-// team): x and the gate are read once.
-template <typename T, bool BLOCK, int PER>
+// The same with a group's values held in registers between the sum of squares and the scaling (PER accesses of V values
+// per member of the team): x and the gate are read once.  V = 4: 16-byte reads of x, 8- or 16-byte accesses of the gate
+// and the output (the group's size, the weight's length and the row strides are multiples of 4, the pointers aligned).
+template <typename T, int V> struct alignas(sizeof(T) * V) NormVec { T v[V]; };
+
+template <typename T, bool BLOCK, int PER, int V>
 __global__ void __launch_bounds__(BLOCK ? 256 : 128) grouped_gated_norm_reg_kernel(
     T* __restrict__ out, long long out_stride, const float* __restrict__ x, long long x_stride, const T* __restrict__ gate,
     long long gate_stride, const float* __restrict__ w, int wlen, int n, int n_groups, int gsize, float eps, int gate_silu,
@@ -410,27 +413,44 @@ __global__ void __launch_bounds__(BLOCK ? 256 : 128) grouped_gated_norm_reg_kern
   const int t = team / n_groups, grp = team % n_groups;
   const float* xr = x + (size_t)t * x_stride + (size_t)grp * gsize;
   const T* gr = gate ? gate + (size_t)t * gate_stride + (size_t)grp * gsize : nullptr;
-  float v[PER], gv[PER];
+  float v[PER][V], gv[PER][V];
   float ss = 0.f;
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
-    const int i = me + step * j;
-    v[j] = i < gsize ? xr[i] : 0.f;
-    gv[j] = 1.f;
-    if (gr && i < gsize) { const float z = to_f32(gr[i]); gv[j] = gate_silu ? silu_f(z) : sigmoid_f(z); }
-    if (gate_first) v[j] *= gv[j];
-    ss = fmaf(v[j], v[j], ss);
+    const int i = (me + step * j) * V;
+    NormVec<float, V> xv;
+    NormVec<T, V> zv;
+    if (i < gsize) {
+      xv = *reinterpret_cast<const NormVec<float, V>*>(xr + i);
+      if (gr) zv = *reinterpret_cast<const NormVec<T, V>*>(gr + i);
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      v[j][e] = i < gsize ? xv.v[e] : 0.f;
+      gv[j][e] = 1.f;
+      if (gr && i < gsize) { const float z = to_f32(zv.v[e]); gv[j][e] = gate_silu ? silu_f(z) : sigmoid_f(z); }
+      if (gate_first) v[j][e] *= gv[j][e];
+      ss = fmaf(v[j][e], v[j][e], ss);
+    }
   }
   ss = BLOCK ? block_sum(ss, scratch) : warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / (float)gsize + eps);
   T* o = out + (size_t)t * out_stride + (size_t)grp * gsize;
+  const int w0 = (int)(((long long)grp * gsize) % wlen);
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
-    const int i = me + step * j;
+    const int i = (me + step * j) * V;
     if (i < gsize) {
-      float r = (v[j] * inv) * w[(grp * gsize + i) % wlen];
-      if (!gate_first) r *= gv[j];
-      o[i] = from_f32<T>(r);
+      int wi = w0 + i;                              // the weight repeats after wlen columns
+      if (wi >= wlen) wi %= wlen;
+      NormVec<T, V> ov;
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        float r = (v[j][e] * inv) * w[wi + e];
+        if (!gate_first) r *= gv[j][e];
+        ov.v[e] = from_f32<T>(r);
+      }
+      *reinterpret_cast<NormVec<T, V>*>(o + i) = ov;
     }
   }
 }
@@ -507,23 +527,22 @@ LMSF_API int lmsf_grouped_gated_norm(void* out, long long out_stride, const floa
   const long long teams = (long long)n * n_groups;
   const bool block = gsize > 1024;
   const unsigned blocks = (unsigned)(block ? teams : (teams + 3) / 4);
-  const int per = ceil_div(gsize, block ? 256 : 32);
-#define LMSF_REG(T, B, P) grouped_gated_norm_reg_kernel<T, B, P><<<blocks, B ? 256 : 128, 0, s>>>((T*)out, out_stride, x, x_stride, (const T*)gate, gate_stride, w, wlen, n, n_groups, gsize, eps, gate_silu, gate_first)
-#define LMSF_PICK(T)                                                                         \
-  if (!block) {                                                                              \
-    if (per <= 2) { LMSF_REG(T, false, 2); return LMSF_LAUNCH_STATUS(); }                     \
-    if (per <= 4) { LMSF_REG(T, false, 4); return LMSF_LAUNCH_STATUS(); }                     \
-    if (per <= 8) { LMSF_REG(T, false, 8); return LMSF_LAUNCH_STATUS(); }                     \
-    if (per <= 16) { LMSF_REG(T, false, 16); return LMSF_LAUNCH_STATUS(); }                   \
-    LMSF_REG(T, false, 32); return LMSF_LAUNCH_STATUS();                                      \
-  } else if (per <= 32) {                                                                    \
-    if (per <= 8) { LMSF_REG(T, true, 8); return LMSF_LAUNCH_STATUS(); }                      \
-    if (per <= 16) { LMSF_REG(T, true, 16); return LMSF_LAUNCH_STATUS(); }                    \
-    LMSF_REG(T, true, 32); return LMSF_LAUNCH_STATUS();                                       \
-  }
+  const size_t esz = dtype == LMSF_F32 ? 4 : 2;
+  const bool wide = gsize % 4 == 0 && wlen % 4 == 0 && x_stride % 4 == 0 && out_stride % 4 == 0 && (!gate || gate_stride % 4 == 0) &&
+                    ((uintptr_t)x | (uintptr_t)w) % 16 == 0 && ((uintptr_t)out | (uintptr_t)gate) % (4 * esz) == 0;
+  const int per = ceil_div(gsize, (block ? 256 : 32) * (wide ? 4 : 1));
+#define LMSF_REG(T, B, P, V) grouped_gated_norm_reg_kernel<T, B, P, V><<<blocks, B ? 256 : 128, 0, s>>>((T*)out, out_stride, x, x_stride, (const T*)gate, gate_stride, w, wlen, n, n_groups, gsize, eps, gate_silu, gate_first)
+#define LMSF_CASE(T, B, P) if (per <= P) { if (wide) LMSF_REG(T, B, P, 4); else LMSF_REG(T, B, P, 1); return LMSF_LAUNCH_STATUS(); }
+#define LMSF_NARROW(T, B, P) if (!wide && per <= P) { LMSF_REG(T, B, P, 1); return LMSF_LAUNCH_STATUS(); }
+#define LMSF_PICK(T)                                                                          \
+  if (!block) { LMSF_CASE(T, false, 1) LMSF_CASE(T, false, 2) LMSF_CASE(T, false, 4) LMSF_CASE(T, false, 8)  \
+                LMSF_NARROW(T, false, 16) LMSF_NARROW(T, false, 32) }                          \
+  else { LMSF_CASE(T, true, 2) LMSF_CASE(T, true, 4) LMSF_NARROW(T, true, 8) LMSF_NARROW(T, true, 16) LMSF_NARROW(T, true, 32) }
   if (dtype == LMSF_F32) { LMSF_PICK(float) }
   else if (dtype == LMSF_BF16) { LMSF_PICK(bf16) }
 #undef LMSF_PICK
+#undef LMSF_NARROW
+#undef LMSF_CASE
 #undef LMSF_REG
 #define LMSF_GO(T, B) grouped_gated_norm_kernel<T, B><<<blocks, B ? 256 : 128, 0, s>>>((T*)out, out_stride, x, x_stride, (const T*)gate, gate_stride, w, wlen, n, n_groups, gsize, eps, gate_silu, gate_first)
   if (dtype == LMSF_F32) { if (block) LMSF_GO(float, true); else LMSF_GO(float, false); }
