@@ -63,7 +63,7 @@ class RedaraxConfig:
     eps: float
     residual_mult: float
     layers: List[RedaraxLayer]
-    side_dim: int = 0                 # 0: no per-layer token input
+    side_dim: int = 0                 # 0: no side branch
     logit_scale: float = 1.0
     logit_softcap: float = 0.0        # 0: no cap
     max_model_len: int = 1 << 20      # angles are computed from the position: bounded by the cache alone

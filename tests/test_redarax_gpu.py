@@ -538,3 +538,78 @@ def test_greedy_generation_through_the_engine():
             if got != nxt:                             # only a near tie may be decided otherwise
                 assert float(lg[nxt] - lg[got]) <= 1e-4 * float(lg.abs().max())
             toks.append(got)
+
+
+# ----------------------------------------------------------------------------- random configurations
+
+def random_config(seed):
+    """Sizes that are no multiples of anything in particular: widths that 8 does not divide, odd head counts, key and value
+    sizes of their own, every optional piece present or absent by chance, the three mixers in any order."""
+    import random
+    from redarax_configs import attention, delta, dense, layer, mamba2, moe
+    rng = random.Random(seed)
+    width = rng.choice([36, 50, 72, 100, 136])
+    layers = []
+    for _ in range(rng.randint(2, 5)):
+        kind = rng.choice(["attention", "mamba2", "delta"])
+        if kind == "attention":
+            kv = rng.randint(1, 3)
+            dim = rng.choice([8, 12, 16, 24, 40, 64])
+            rot = rng.choice([None, 2, dim // 2 // 2 * 2, dim])
+            mixer = attention(kv * rng.randint(1, 3), kv, dim, rng.choice([8, 16, 20, 40, 64]), rng.choice([0.1, 0.3, dim ** -0.5]),
+                              rot or None, rng.choice([50.0, 10000.0, 1.0e6]))
+        elif kind == "mamba2":
+            groups = rng.randint(1, 2)
+            heads = groups * rng.randint(1, 3)
+            vdim = rng.choice([8, 12, 16, 24])
+            # (a norm over a handful of columns that happen to be small amplifies float32 rounding in any implementation:
+            # the groups keep at least eight columns)
+            parts = rng.choice([g for g in (1, 2, 3, heads) if (heads * vdim) % g == 0 and heads * vdim // g >= 8])
+            mixer = mamba2(heads, vdim, rng.choice([3, 8, 16, 33, 70]), groups, parts, rng.randint(1, 4))
+        else:
+            kv = rng.randint(1, 3)
+            mixer = delta(kv * rng.randint(1, 2), kv, rng.choice([4, 10, 16, 36, 72]), rng.choice([9, 16, 33, 70]), rng.randint(1, 4))
+        r = rng.random()
+        if r < 0.2:
+            mlp = None
+        elif r < 0.45:
+            mlp = dense(rng.choice([8, 20, 44]), rng.choice([0.5, 1.5, 7.0]))
+        else:
+            count = rng.randint(1, 3)
+            size = rng.randint(1, 3)
+            keep = rng.randint(1, count)
+            top = rng.randint(1, keep * size)
+            mlp = moe(count * size, top, rng.choice([8, 12, 20, 40]), rng.choice([0.5, 1.5, 7.0]), count if rng.random() < 0.8 else None, keep)
+            if "groups" not in mlp["router"]:
+                mlp["router"]["top"] = rng.randint(1, count * size)
+        layers.append(layer(mixer, mlp))
+    cfg = {"architecture": "Redarax", "vocab": rng.choice([61, 128, 257]), "width": width, "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-3])},
+           "residual_mult": rng.choice([0.25, 0.7, 1.0, 1.4]), "layers": layers}
+    if rng.random() < 0.7:
+        cfg["token_side"] = {"dim": rng.choice([1, 4, 10, 16])}
+    if rng.random() < 0.6:
+        cfg["logit_scale"] = rng.choice([0.5, 2.0, 3.0])
+    if rng.random() < 0.6:
+        cfg["logit_softcap"] = rng.choice([5.0, 15.0, 50.0])
+    return cfg
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_configurations(seed):
+    import random
+    name = f"R{seed}"
+    CONFIGS[name] = random_config(seed)
+    folder, _ = folder_of(name)
+    rng = random.Random(seed)
+    reqs = requests_for(name, [rng.randint(1, 70) for _ in range(4)], seed=seed)
+    ref = oracle(name, reqs)
+    bs = rng.choice([8, 16, 32])
+    for dtype in ("float32", "bfloat16"):
+        for steps in (traces.whole(reqs, tail=5), traces.mixed(reqs, seed=seed, max_live=2, tail=4)):
+            out = traces.run_inprocess(folder, dtype, steps, bs, traces.max_live_tokens(steps, 64), max_live=2)
+            rows = traces.collect(steps, out)
+            if dtype == "float32":
+                assert worst_rel(rows, ref) <= 5e-5, (CONFIGS[name], worst_rel(rows, ref))
+            else:
+                e = position_errors(rows, ref)
+                assert e[len(e) // 2] <= 4e-2, (CONFIGS[name], e[len(e) // 2])
