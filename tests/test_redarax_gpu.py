@@ -603,13 +603,18 @@ def test_random_configurations(seed):
     rng = random.Random(seed)
     reqs = requests_for(name, [rng.randint(1, 70) for _ in range(4)], seed=seed)
     ref = oracle(name, reqs)
+    # how far the plain implementation itself moves when it is run in float32: a norm over a few small values, or a gate
+    # that passes through zero, amplifies rounding in any implementation (about one configuration in twenty)
+    _, w = folder_of(name)
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    cond = max(float(np.abs(P.forward(CONFIGS[name], w, toks, dtype=torch.float32).numpy() - ref[rid]).max()) for rid, toks in reqs.items()) / scale
     bs = rng.choice([8, 16, 32])
     for dtype in ("float32", "bfloat16"):
         for steps in (traces.whole(reqs, tail=5), traces.mixed(reqs, seed=seed, max_live=2, tail=4)):
             out = traces.run_inprocess(folder, dtype, steps, bs, traces.max_live_tokens(steps, 64), max_live=2)
             rows = traces.collect(steps, out)
             if dtype == "float32":
-                assert worst_rel(rows, ref) <= 5e-5, (CONFIGS[name], worst_rel(rows, ref))
+                assert worst_rel(rows, ref) <= max(5e-5, 3 * cond), (CONFIGS[name], worst_rel(rows, ref), cond)
             else:
                 e = position_errors(rows, ref)
                 assert e[len(e) // 2] <= 4e-2, (CONFIGS[name], e[len(e) // 2])
